@@ -1,0 +1,401 @@
+"""TEST INFRASTRUCTURE ONLY -- CPU checker for the CUDA library.
+
+Two interchangeable back ends compute the op arithmetic:
+
+* ``port``: ``oracle/_build/liboracle.so``, this repository's plain-C
+  restatement (``hgc_oracle.c``);
+* ``ref``:  ``oracle/_ref/libref.so``, the reference's own CPU kernels compiled
+  from a cms-pepr/HGCalML checkout (only present where that was built).
+
+On top of either, this module restates in numpy float32 the TensorFlow glue of
+the reference's Python wrappers (min-shift, bin width, stable argsort, gathers,
+cumsum, index remap, scatter back), citing the wrapper lines it follows.
+
+Only ``tests/``, the smoke check and the CPU-baseline leg of ``bench.py`` may
+import this module; the product never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import subprocess
+from ctypes import POINTER, c_float, c_int
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PORT_SO = os.path.join(_HERE, "_build", "liboracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libref.so")
+
+_fp = POINTER(c_float)
+_ip = POINTER(c_int)
+
+
+def build(quiet: bool = True) -> None:
+    """Compile the checker libraries (the reference one only where a checkout exists)."""
+    subprocess.run(["make", "-C", _HERE, "all"], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def _f(a):
+    assert a.dtype == np.float32 and a.flags.c_contiguous
+    return a.ctypes.data_as(_fp)
+
+
+def _i(a):
+    assert a.dtype == np.int32 and a.flags.c_contiguous
+    return a.ctypes.data_as(_ip)
+
+
+def _c32f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _c32i(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class _Lib:
+    """ctypes view of one checker library; both export the same five routines."""
+
+    def __init__(self, path: str, prefix: str):
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.path = path
+        self.prefix = prefix
+        self.dll = ctypes.CDLL(path)
+
+    def fn(self, name):
+        return getattr(self.dll, self.prefix + name)
+
+
+_libs: dict = {}
+
+
+def have(backend: str) -> bool:
+    return os.path.exists(_REF_SO if backend == "ref" else _PORT_SO)
+
+
+def lib(backend: str = "port") -> _Lib:
+    if backend not in _libs:
+        if backend == "port":
+            if not os.path.exists(_PORT_SO):
+                subprocess.run(["make", "-C", _HERE, "port"], check=True, stdout=subprocess.DEVNULL)
+            _libs[backend] = _Lib(_PORT_SO, "oracle_")
+        elif backend == "ref":
+            _libs[backend] = _Lib(_REF_SO, "ref_")
+        else:
+            raise ValueError(backend)
+    return _libs[backend]
+
+
+# --------------------------------------------------------------------------
+# op-level calls (raw functor semantics)
+# --------------------------------------------------------------------------
+def op_bin_by_coordinates(coords, row_splits, bin_width, n_bins, calc_n_per_bin=True, backend="port"):
+    """Functor of bin_by_coordinates_kernel.cc:117-156. Returns (bin_assignment, flat, n_per_bin)."""
+    coords = _c32f(coords)
+    row_splits = _c32i(row_splits)
+    bin_width = _c32f(bin_width).reshape(1)
+    n_bins = _c32i(n_bins)
+    n, c = coords.shape
+    total = int(np.prod(n_bins.astype(np.int64))) * (len(row_splits) - 1)
+    assigned = np.zeros((n, c + 1), np.int32)
+    flat = np.zeros((n,), np.int32)
+    nper = np.zeros((total,), np.int32)
+    lib(backend).fn("bin_by_coordinates")(
+        _f(coords), _i(row_splits), _f(bin_width), _i(n_bins), _i(assigned), _i(flat), _i(nper),
+        c_int(n), c_int(c), c_int(len(row_splits)), c_int(total), c_int(int(calc_n_per_bin)))
+    return assigned, flat, nper
+
+
+def op_binned_select_knn(K, coords, bin_idx, dim_bin_idx, bin_boundaries, n_bins, bin_width,
+                         tf_compatible=False, direction=None, backend="port"):
+    """Kernel of binned_select_knn_kernel.cc:47-196 on bin-sorted inputs. Returns (idx, distsq)."""
+    coords = _c32f(coords)
+    bin_idx = _c32i(bin_idx)
+    dim_bin_idx = _c32i(dim_bin_idx)
+    bin_boundaries = _c32i(bin_boundaries)
+    n_bins = _c32i(n_bins)
+    bin_width = _c32f(bin_width).reshape(1)
+    use_direction = direction is not None
+    direction = _c32i(direction if use_direction else np.zeros((0,), np.int32))
+    n, c = coords.shape
+    idx = np.empty((n, K), np.int32)
+    dist = np.empty((n, K), np.float32)
+    rc = lib(backend).fn("binned_select_knn")(
+        _f(coords), _i(bin_idx), _i(direction), _i(dim_bin_idx), _i(bin_boundaries), _i(n_bins),
+        _f(bin_width), _i(idx), _f(dist),
+        c_int(n), c_int(K), c_int(c), c_int(len(n_bins)), c_int(len(bin_boundaries)),
+        c_int(int(tf_compatible)), c_int(int(use_direction)))
+    if rc != 0:
+        raise ValueError("unsupported number of binning dimensions")
+    return idx, dist
+
+
+def op_index_replacer(to_be_replaced, replacements, backend="port"):
+    """Functor of index_replacer_kernel.cc:15-42."""
+    tbr = _c32i(to_be_replaced)
+    rep = _c32i(replacements)
+    out = np.zeros_like(tbr)
+    lib(backend).fn("index_replacer")(_i(tbr.reshape(-1)), _i(rep), _i(out.reshape(-1)),
+                                      c_int(tbr.size), c_int(rep.shape[0]))
+    return out
+
+
+def op_accumulate_knn(weights, features, indices, mean_and_max=True, backend="port"):
+    """Functor of accumulate_knn_kernel.cc:27-83 (weights are used verbatim)."""
+    weights = _c32f(weights)
+    features = _c32f(features)
+    indices = _c32i(indices)
+    n, k = indices.shape
+    f = features.shape[1]
+    n_out = 2 * f if mean_and_max else f
+    out = np.zeros((n, n_out), np.float32)
+    maxidx = np.zeros((n, f), np.int32)
+    fn = lib(backend).fn("accumulate_knn")
+    if backend == "ref":
+        fn(_f(weights), _f(features), _i(indices), _f(out), _i(maxidx),
+           c_int(n), c_int(k), c_int(f), c_int(n_out), c_int(0), c_int(int(mean_and_max)))
+    else:
+        fn(_f(weights), _f(features), _i(indices), _f(out), _i(maxidx),
+           c_int(n), c_int(k), c_int(f), c_int(n_out), c_int(int(mean_and_max)))
+    return out, maxidx
+
+
+def op_binned_assign_to_condensates(ccoords, dist, beta, mask, bins_flat, bin_splits,
+                                    indices_to_filtered, original_indices_h, row_splits, n_bins,
+                                    bin_width, ccoords_h, dist_h, beta_h, mask_h, row_splits_h,
+                                    assign_by_max_beta, backend="port"):
+    """Functor of binned_assign_to_condensates_kernel.cc:128-241.
+    Returns (assigned_h, assigned, alpha_indices, association, n_condensates)."""
+    del bins_flat  # an op input the functor never receives
+    ccoords = _c32f(ccoords)
+    n, dims = ccoords.shape
+    dist = _c32f(dist).reshape(-1)
+    mask = _c32i(mask).reshape(-1)
+    itf = _c32i(indices_to_filtered)
+    orig_h = _c32i(original_indices_h)
+    row_splits = _c32i(row_splits)
+    n_bins = _c32i(n_bins)
+    bin_width = _c32f(bin_width).reshape(1)
+    bin_splits = _c32i(bin_splits)
+    ccoords_h = _c32f(ccoords_h).reshape(-1, dims)
+    dist_h = _c32f(dist_h).reshape(-1)
+    beta_h = _c32f(beta_h).reshape(-1)
+    mask_h = _c32i(mask_h).reshape(-1)
+    row_splits_h = _c32i(row_splits_h)
+    nh = beta_h.shape[0]
+    # The pick loop reads mask_h[0] or mask_h[1] whatever the subset size; pad so it stays in bounds.
+    mask_h_padded = np.concatenate([mask_h, np.zeros(2, np.int32)])
+    claimed_h = np.zeros((nh,), np.int32)
+    assigned_h = np.zeros((nh,), np.int32)
+    assigned = np.zeros((n,), np.int32)
+    asso = np.zeros((n,), np.int32)
+    alpha = np.zeros((nh,), np.int32)
+    ncond = np.zeros((len(row_splits),), np.int32)
+    min_d = np.zeros((n,), np.float32)
+    rc = lib(backend).fn("binned_assign_to_condensates")(
+        c_int(dims), c_int(len(n_bins)), _i(claimed_h), _f(ccoords_h), _f(dist_h), _f(beta_h),
+        _i(mask_h_padded), _i(assigned_h), _i(orig_h), _i(row_splits_h), _f(ccoords), _f(dist), _i(mask),
+        _i(itf), None if assign_by_max_beta else _f(min_d), _i(assigned), _i(asso), _i(ncond),
+        _i(alpha), _i(bin_splits), _i(n_bins), _f(bin_width), _i(row_splits),
+        c_int(len(row_splits) - 1), c_int(int(assign_by_max_beta)))
+    if rc != 0:
+        raise RuntimeError("condensate search made no progress")
+    return assigned_h, assigned, alpha, asso, ncond
+
+
+# --------------------------------------------------------------------------
+# wrapper-level restatements (TensorFlow glue in numpy float32)
+# --------------------------------------------------------------------------
+def BinByCoordinates(coordinates, row_splits, bin_width=None, n_bins=None, calc_n_per_bin=True,
+                     pre_normalized=False, backend="port"):
+    """modules/bin_by_coordinates_op.py:14-88."""
+    coordinates = _c32f(coordinates)
+    if not pre_normalized:
+        coordinates = coordinates - coordinates.min(axis=0, keepdims=True)
+    dmax = coordinates.max(axis=0)
+    dmin = coordinates.min(axis=0)
+    dmax = (np.where(dmin == dmax, dmax + np.float32(1.), dmax) + np.float32(1e-3)).astype(np.float32)
+    dmax = np.where(np.isfinite(dmax), dmax, np.float32(1.)).astype(np.float32)
+    if bin_width is None:
+        assert n_bins is not None
+        bin_width = (dmax / np.float32(n_bins)).astype(np.float32)
+        n_bins = None
+        bin_width = np.array([bin_width.max()], np.float32)
+    else:
+        bin_width = _c32f(bin_width).reshape(1)
+    if n_bins is None:
+        nb = (dmax / bin_width).astype(np.float32) + np.float32(1.)
+        n_bins = nb.astype(np.int32)
+    else:
+        n_bins = _c32i(n_bins)
+    binass, flat, nper = op_bin_by_coordinates(coordinates, row_splits, bin_width, n_bins,
+                                               calc_n_per_bin, backend)
+    if calc_n_per_bin:
+        return binass, flat, n_bins, bin_width, nper
+    return binass, flat, n_bins, bin_width
+
+
+def default_n_bins(first_event_size: int, K: int, dims: int) -> int:
+    """modules/binned_select_knn_op.py:59-63 (float32 pow, truncation, clamp to [5, 30])."""
+    nb = np.power(np.float32(first_event_size) / np.float32(K / 32), np.float32(1 / dims), dtype=np.float32)
+    return int(min(max(int(nb), 5), 30))
+
+
+def BinnedSelectKnn(K, coords, row_splits, direction=None, n_bins=None, max_bin_dims=3,
+                    tf_compatible=False, backend="port", return_sorting=False):
+    """modules/binned_select_knn_op.py:32-95 with the TF-gradient branch off (globals.py:91)."""
+    coords = _c32f(coords)
+    row_splits = _c32i(row_splits)
+    max_bin_dims = min(max_bin_dims, coords.shape[1])
+    if n_bins is None:
+        n_bins = default_n_bins(int(row_splits[1]), K, max_bin_dims)
+    bin_coords = coords[:, :max_bin_dims]
+    dbinning, binning, nb, bin_width, nper = BinByCoordinates(bin_coords, row_splits, n_bins=n_bins,
+                                                              backend=backend)
+    sorting = np.argsort(binning, kind="stable").astype(np.int32)
+    scoords = coords[sorting]
+    sbinning = binning[sorting]
+    sdbinning = dbinning[sorting]
+    sdirection = None if direction is None else _c32i(direction)[sorting]
+    bin_boundaries = np.concatenate([np.zeros(1, np.int32), nper]).cumsum().astype(np.int32)
+    idx_s, dist_s = op_binned_select_knn(K, scoords, sbinning, sdbinning, bin_boundaries, nb, bin_width,
+                                         tf_compatible, sdirection, backend)
+    idx_r = op_index_replacer(idx_s, sorting, backend)
+    dist = np.zeros_like(dist_s)
+    idx = np.zeros_like(idx_r)
+    dist[sorting] = dist_s
+    idx[sorting] = idx_r
+    dist = np.where(idx < 0, np.float32(0.), dist).astype(np.float32)
+    if return_sorting:
+        return idx, dist, sorting
+    return idx, dist
+
+
+def AccumulateKnn(distances, features, indices, mean_and_max=True, backend="port"):
+    """modules/accknn_op.py:39-58: weights = exp(-distances) in float32, then the op."""
+    w = np.exp(-_c32f(distances)).astype(np.float32)
+    return op_accumulate_knn(w, features, indices, mean_and_max, backend)
+
+
+def AccumulateLinKnn(weights, features, indices, mean_and_max=True, backend="port"):
+    """modules/accknn_op.py:17-36: the op on the weights as given."""
+    return op_accumulate_knn(weights, features, indices, mean_and_max, backend)
+
+
+def _segment_ids_to_row_splits(ids, num_segments):
+    counts = np.bincount(ids, minlength=num_segments).astype(np.int64)
+    return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+
+
+def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_threshold,
+                                    no_condensation_mask=None, distance_threshold=1.,
+                                    assign_by_max_beta=False, nbin_dims=3, backend="port",
+                                    return_op_io=False):
+    """modules/assign_condensate_op.py:210-333 without the keep_noise post-processing.
+    Returns (assignment[N,1], association[N], alpha_idx, is_cond[N,1], n_condensates)."""
+    ccoords = _c32f(ccoords)
+    betas = _c32f(betas).reshape(-1, 1)
+    dist = (_c32f(dist).reshape(-1, 1) / np.float32(distance_threshold)).astype(np.float32)
+    row_splits = _c32i(row_splits)
+    num_rows = len(row_splits) - 1
+    n = ccoords.shape[0]
+    if no_condensation_mask is None:
+        no_condensation_mask = np.zeros((n, 1), np.int32)
+    mask = _c32i(no_condensation_mask).reshape(-1, 1)
+
+    nvertmax = int(row_splits[-1] - row_splits[0])
+    n_bins_sc = max(4, min(int(math.ceil(math.pow(nvertmax / 5, 1 / 3))), 25))
+    ccoords = ccoords - ccoords.min(axis=0, keepdims=True)
+    cc2 = ccoords[:, :min(ccoords.shape[1], nbin_dims)]
+    _, bins_flat, n_bins, bin_width = BinByCoordinates(cc2, row_splits, n_bins=n_bins_sc,
+                                                       calc_n_per_bin=False, pre_normalized=True,
+                                                       backend=backend)
+    sorting = np.argsort(bins_flat, kind="stable").astype(np.int32)
+    sorting_back = np.argsort(sorting, kind="stable")
+    ccoords = ccoords[sorting]
+    betas = betas[sorting]
+    dist = dist[sorting]
+    mask = mask[sorting]
+    bins_flat = bins_flat[sorting]
+    orig = np.arange(n, dtype=np.int32)[sorting]
+    total_bins = int(np.prod(n_bins.astype(np.int64))) * num_rows
+    bin_splits = _segment_ids_to_row_splits(bins_flat, total_bins)
+
+    high = np.logical_or(betas > np.float32(beta_threshold), mask > 0)[:, 0]
+    seg = np.repeat(np.arange(num_rows), np.diff(row_splits))
+    row_splits_h = _segment_ids_to_row_splits(seg[high], num_rows)
+    betas_h, ccoords_h, dist_h = betas[high], ccoords[high], dist[high]
+    mask_h, orig_h = mask[high], orig[high]
+    itf = np.full((n,), -1, np.int32)
+    itf[np.nonzero(high)[0]] = np.arange(int(high.sum()), dtype=np.int32)
+
+    op_in = dict(ccoords=ccoords, dist=dist, beta=betas, mask=mask, bins_flat=bins_flat,
+                 bin_splits=bin_splits, indices_to_filtered=itf, original_indices_h=orig_h,
+                 row_splits=row_splits, n_bins=n_bins, bin_width=bin_width, ccoords_h=ccoords_h,
+                 dist_h=dist_h, beta_h=betas_h, mask_h=mask_h, row_splits_h=row_splits_h,
+                 assign_by_max_beta=assign_by_max_beta)
+    assigned_h, assignment_s, alpha, asso_s, ncond = op_binned_assign_to_condensates(**op_in, backend=backend)
+    assignment = assignment_s[sorting_back]
+    asso = asso_s[sorting_back]
+    alpha_idx = alpha[alpha != -1]
+    is_cond = np.zeros((n,), bool)
+    is_cond[alpha_idx] = True
+    out = (assignment[:, None], asso, alpha_idx, is_cond[:, None], ncond)
+    if return_op_io:
+        return out, op_in, (assigned_h, assignment_s, alpha, asso_s, ncond)
+    return out
+
+
+# --------------------------------------------------------------------------
+# parity helpers
+# --------------------------------------------------------------------------
+def canonical_knn(idx, dist):
+    """Row-wise canonical order: slot 0 stays (the query itself), the other slots are sorted by
+    (distance, index) ascending with the -1 padding last.  The reference's own comparison op
+    treats rows as sets (compare_knn_outputs_kernel.cc:42-60)."""
+    idx = np.asarray(idx)
+    dist = np.asarray(dist)
+    n, k = idx.shape
+    if k <= 1:
+        return idx.copy(), dist.copy()
+    pad = idx[:, 1:] < 0
+    bits = dist[:, 1:].astype(np.float32).view(np.uint32).astype(np.uint64)
+    key = (bits << np.uint64(32)) | idx[:, 1:].astype(np.int64).astype(np.uint64) & np.uint64(0xFFFFFFFF)
+    key = np.where(pad, np.uint64(0xFFFFFFFFFFFFFFFF), key)
+    order = np.argsort(key, axis=1, kind="stable")
+    ci = np.concatenate([idx[:, :1], np.take_along_axis(idx[:, 1:], order, axis=1)], axis=1)
+    cd = np.concatenate([dist[:, :1], np.take_along_axis(dist[:, 1:], order, axis=1)], axis=1)
+    return ci, cd
+
+
+def brute_force_knn(K, coords, row_splits, max_rows=None, rows=None):
+    """Definitional kNN (float32, the reference's distance expression and summation order,
+    ties broken by index) for the given query rows; canonical row order."""
+    coords = _c32f(coords)
+    row_splits = np.asarray(row_splits)
+    n = coords.shape[0]
+    if rows is None:
+        rows = np.arange(n)
+        if max_rows is not None and n > max_rows:
+            rows = np.random.default_rng(0).choice(n, max_rows, replace=False)
+    out_i = np.full((len(rows), K), -1, np.int32)
+    out_d = np.zeros((len(rows), K), np.float32)
+    ev = np.searchsorted(row_splits, rows, side="right") - 1
+    for r, (q, e) in enumerate(zip(rows, ev)):
+        lo, hi = int(row_splits[e]), int(row_splits[e + 1])
+        d = np.zeros((hi - lo,), np.float32)
+        for c in range(coords.shape[1]):
+            t = coords[q, c] - coords[lo:hi, c]
+            d = d + t * t
+        ids = np.arange(lo, hi)
+        keep = ids != q
+        d, ids = d[keep], ids[keep]
+        order = np.lexsort((ids, d))[:K - 1]
+        out_i[r, 0] = q
+        out_i[r, 1:1 + len(order)] = ids[order]
+        out_d[r, 1:1 + len(order)] = d[order]
+    return rows, out_i, out_d
