@@ -1,0 +1,240 @@
+// Grid binning of hits: per-hit bin keys, the batch-global coordinate range, and the histogram
+// (hits per bin) obtained from the sorted keys instead of from atomics.
+#include "common.cuh"
+#include "binning.cuh"
+
+namespace hgc {
+
+// ---- per-hit keys ---------------------------------------------------------------------------
+// Follows modules/compiled/bin_by_coordinates_kernel.cc:64-113: truncating float division per
+// dimension (last dimension fastest), out-of-range indices forced to 0, event index above all.
+// `shift` (may be null) is subtracted from the coordinates first, as the Python wrapper does
+// before calling the op (modules/bin_by_coordinates_op.py:49-52).
+__global__ void bin_keys_kernel(const float *__restrict__ coords, int coord_stride, int n_dims,
+                                const float *__restrict__ shift,
+                                const int *__restrict__ row_splits, int n_rs,
+                                const float *__restrict__ bin_width, const int *__restrict__ n_bins,
+                                int *__restrict__ assigned, int *__restrict__ flat_out,
+                                int *__restrict__ sort_keys, int n_vert, int n_total_bins,
+                                const int *__restrict__ n_total_bins_dev, unsigned *status)
+{
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n_vert) return;
+    const float bw = bin_width[0];
+    const int total = n_total_bins_dev ? n_total_bins_dev[0] : n_total_bins;
+    int stride = 1, flat = 0;
+    for (int c = n_dims - 1; c >= 0; c--) {
+        float x = coords[(size_t)v * coord_stride + c];
+        if (shift) x = __fsub_rn(x, shift[c]);
+        int ci = __float2int_rz(__fdiv_rn(x, bw));
+        const int nb = n_bins[c];
+        if (ci < 0 || ci >= nb) {
+            ci = 0;
+            flag_status(status, HGC_STATUS_BIN_OUT_OF_RANGE);
+        }
+        if (assigned) assigned[(size_t)v * (n_dims + 1) + c + 1] = ci;
+        flat += ci * stride;
+        stride *= nb;
+    }
+    // event = number of row_splits[1..n_rs-1] that are <= v (row splits ascend)
+    int lo = 1, hi = n_rs;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (row_splits[mid] <= v) lo = mid + 1; else hi = mid;
+    }
+    const int event = lo - 1;
+    flat += event * stride;
+    if (flat >= total || flat < 0) {
+        flag_status(status, HGC_STATUS_FLAT_BIN_OVERFLOW);
+        if (sort_keys) sort_keys[v] = total;  // sentinel: sorts last, belongs to no bin
+        return;
+    }
+    if (assigned) assigned[(size_t)v * (n_dims + 1)] = event;
+    if (flat_out) flat_out[v] = flat;
+    if (sort_keys) sort_keys[v] = flat;
+}
+
+__global__ void adjacent_difference_kernel(const int *__restrict__ bounds, int *__restrict__ out, int n)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = bounds[i + 1] - bounds[i];
+}
+
+// ---- batch-global min / max of the first n_dims coordinates -----------------------------------
+
+__global__ void __launch_bounds__(256)
+range_partial_kernel(const float *__restrict__ coords, int coord_stride, int n_dims, int n_vert,
+                     float *__restrict__ partial /* [gridDim.x][2][kMaxBinDims] */)
+{
+    float mn[kMaxBinDims], mx[kMaxBinDims];
+#pragma unroll
+    for (int c = 0; c < kMaxBinDims; c++) { mn[c] = INFINITY; mx[c] = -INFINITY; }
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vert; v += gridDim.x * blockDim.x) {
+#pragma unroll
+        for (int c = 0; c < kMaxBinDims; c++)
+            if (c < n_dims) {
+                const float x = coords[(size_t)v * coord_stride + c];
+                mn[c] = fminf(mn[c], x);
+                mx[c] = fmaxf(mx[c], x);
+            }
+    }
+    __shared__ float s_mn[8][kMaxBinDims], s_mx[8][kMaxBinDims];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int c = 0; c < kMaxBinDims; c++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn[c] = fminf(mn[c], __shfl_xor_sync(0xffffffffu, mn[c], o));
+            mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], o));
+        }
+        if (lane == 0) { s_mn[warp][c] = mn[c]; s_mx[warp][c] = mx[c]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < kMaxBinDims) {
+        const int c = threadIdx.x;
+        float a = s_mn[0][c], b = s_mx[0][c];
+        for (int w = 1; w < 8; w++) { a = fminf(a, s_mn[w][c]); b = fmaxf(b, s_mx[w][c]); }
+        partial[((size_t)blockIdx.x * 2 + 0) * kMaxBinDims + c] = a;
+        partial[((size_t)blockIdx.x * 2 + 1) * kMaxBinDims + c] = b;
+    }
+}
+
+// One block: finishes the min/max reduction and derives the grid exactly as the Python wrappers do
+// (modules/bin_by_coordinates_op.py:49-71, modules/binned_select_knn_op.py:57-63), in float32.
+__global__ void __launch_bounds__(32)
+grid_setup_kernel(const float *__restrict__ partial, int n_partials, int n_dims,
+                  const int *__restrict__ row_splits, int n_rs, int n_bins_arg, int n_neigh,
+                  int pre_normalized, GridParams *__restrict__ g)
+{
+    const int c = threadIdx.x;
+    float mn = 0.f, mx = 0.f;
+    if (c < n_dims) {
+        mn = INFINITY; mx = -INFINITY;
+        for (int p = 0; p < n_partials; p++) {
+            mn = fminf(mn, partial[((size_t)p * 2 + 0) * kMaxBinDims + c]);
+            mx = fmaxf(mx, partial[((size_t)p * 2 + 1) * kMaxBinDims + c]);
+        }
+    }
+    // The wrapper shifts by the minimum first; x -> x - mn is monotone, so the shifted extremes
+    // are the extremes shifted.
+    const float shift = pre_normalized ? 0.f : mn;
+    const float smin = __fsub_rn(mn, shift);
+    float dmax = __fsub_rn(mx, shift);
+    if (smin == dmax) dmax = __fadd_rn(dmax, 1.f);
+    dmax = __fadd_rn(dmax, 1e-3f);
+    if (!isfinite(dmax)) dmax = 1.f;
+
+    int n_bins = n_bins_arg;
+    if (n_bins <= 0) {
+        const float first_event = n_rs > 1 ? (float)row_splits[1] : 1.f;
+        const float t = powf(__fdiv_rn(first_event, (float)n_neigh / 32.f), 1.f / (float)n_dims);
+        n_bins = (int)t;
+        n_bins = n_bins < 5 ? 5 : (n_bins > 30 ? 30 : n_bins);
+    }
+    float bw = c < n_dims ? __fdiv_rn(dmax, (float)n_bins) : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bw = fmaxf(bw, __shfl_xor_sync(0xffffffffu, bw, o));
+    int nb = 1;
+    if (c < n_dims) nb = (int)__fadd_rn(__fdiv_rn(dmax, bw), 1.f);
+    int prod = nb;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) prod *= __shfl_xor_sync(0xffffffffu, prod, o);
+    if (c < n_dims) { g->shift[c] = shift; g->n_bins[c] = nb; }
+    if (c == 0) {
+        g->bin_width = bw;
+        g->bins_per_event = prod;
+        g->n_total_bins = prod * (n_rs - 1);
+    }
+}
+
+int compute_grid(const float *coords, int coord_stride, int n_dims, int n_vert,
+                 const int *row_splits, int n_rs, int n_bins_arg, int n_neigh, int pre_normalized,
+                 float *partial, GridParams *grid, cudaStream_t stream)
+{
+    const int blocks = range_partial_blocks(n_vert);
+    range_partial_kernel<<<blocks, 256, 0, stream>>>(coords, coord_stride, n_dims, n_vert, partial);
+    HGC_LAUNCH_CHECK();
+    grid_setup_kernel<<<1, 32, 0, stream>>>(partial, blocks, n_dims, row_splits, n_rs, n_bins_arg,
+                                           n_neigh, pre_normalized, grid);
+    HGC_LAUNCH_CHECK();
+    return HGC_OK;
+}
+
+int range_partial_blocks(int n_vert)
+{
+    int b = div_up(n_vert > 0 ? n_vert : 1, 256 * 8);
+    return b > 2 * kNumSMs ? 2 * kNumSMs : b;
+}
+
+int launch_bin_keys(const float *coords, int coord_stride, int n_dims, const float *shift,
+                    const int *row_splits, int n_rs, const float *bin_width, const int *n_bins,
+                    int *assigned, int *flat_out, int *sort_keys, int n_vert, int n_total_bins,
+                    const int *n_total_bins_dev, unsigned *status, cudaStream_t stream)
+{
+    if (n_vert <= 0) return HGC_OK;
+    bin_keys_kernel<<<div_up(n_vert, 256), 256, 0, stream>>>(
+            coords, coord_stride, n_dims, shift, row_splits, n_rs, bin_width, n_bins, assigned, flat_out,
+            sort_keys, n_vert, n_total_bins, n_total_bins_dev, status);
+    HGC_LAUNCH_CHECK();
+    return HGC_OK;
+}
+
+}  // namespace hgc
+
+using namespace hgc;
+
+extern "C" size_t hgc_bin_by_coordinates_workspace_bytes(int n_vert, int n_coords, int n_rs, int n_total_bins)
+{
+    (void)n_coords; (void)n_rs;
+    Sizer s;
+    const size_t n = n_vert > 0 ? n_vert : 0;
+    s.take<int>(n);                                   // sort keys
+    s.take<int>(n); s.take<int>(n);                   // sorted keys / values
+    s.take<int>(n); s.take<int>(n);                   // ping-pong
+    s.take<int>(sort_hist_ints(n_vert));
+    s.take<int>((size_t)(n_total_bins > 0 ? n_total_bins : 0) + 1);
+    return s.used;
+}
+
+extern "C" int hgc_bin_by_coordinates(
+        const float *d_coords, const int *d_row_splits, const float *d_bin_width, const int *d_n_bins,
+        int *d_assigned_bin, int *d_flat_assigned_bin, int *d_n_per_bin,
+        int n_vert, int n_coords, int n_rs, int n_total_bins, int calc_n_per_bin,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n_vert < 0 || n_coords < 1 || n_rs < 1 || n_total_bins < 0) return HGC_ERR_INVALID_ARGUMENT;
+    if (n_coords > kMaxBinDims) return HGC_ERR_UNSUPPORTED;
+    if (!d_bin_width || !d_n_bins || !d_row_splits || (n_vert > 0 && (!d_coords || !d_assigned_bin || !d_flat_assigned_bin)))
+        return HGC_ERR_INVALID_ARGUMENT;
+    if (n_total_bins > 0 && !d_n_per_bin) return HGC_ERR_INVALID_ARGUMENT;
+    const size_t need = hgc_bin_by_coordinates_workspace_bytes(n_vert, n_coords, n_rs, n_total_bins);
+    if (int rc = check_workspace(workspace, workspace_bytes, need)) return rc;
+
+    Carver ws(workspace);
+    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
+    const size_t n = n_vert;
+    int *keys = ws.take<int>(n);
+    int *skeys = ws.take<int>(n), *svals = ws.take<int>(n);
+    int *tkeys = ws.take<int>(n), *tvals = ws.take<int>(n);
+    int *hist = ws.take<int>(sort_hist_ints(n_vert));
+    int *bounds = ws.take<int>((size_t)n_total_bins + 1);
+
+    const bool histogram = calc_n_per_bin != 0 && n_total_bins > 0;
+    if (int rc = launch_bin_keys(d_coords, n_coords, n_coords, nullptr, d_row_splits, n_rs, d_bin_width,
+                                 d_n_bins, d_assigned_bin, d_flat_assigned_bin, histogram ? keys : nullptr,
+                                 n_vert, n_total_bins, nullptr, ws.status(), stream))
+        return rc;
+    if (n_total_bins == 0) return HGC_OK;
+    if (!histogram) {
+        HGC_CUDA_TRY(cudaMemsetAsync(d_n_per_bin, 0, sizeof(int) * (size_t)n_total_bins, stream));
+        return HGC_OK;
+    }
+    if (int rc = sort_pairs(keys, nullptr, skeys, svals, tkeys, tvals, hist, n_vert,
+                            bits_for(n_total_bins), stream))
+        return rc;
+    if (int rc = boundaries_from_sorted_keys(skeys, n_vert, bounds, n_total_bins, stream)) return rc;
+    adjacent_difference_kernel<<<div_up(n_total_bins, 256), 256, 0, stream>>>(bounds, d_n_per_bin, n_total_bins);
+    HGC_LAUNCH_CHECK();
+    return HGC_OK;
+}

@@ -1,0 +1,174 @@
+/*
+ * hgcalml_b200 -- C ABI of the sm_100a CUDA library behind the HGCalML custom ops of the
+ * GravNet / object-condensation inference path.
+ *
+ * Conventions
+ *  - Every pointer whose name starts with d_ is DEVICE memory; all tensors are dense,
+ *    row-major, float32 or int32, exactly as the TensorFlow ops receive them.
+ *  - The library allocates nothing that the caller sees: scratch memory is passed in
+ *    (`workspace`, sized by the matching *_workspace_bytes query; 256-byte aligned).
+ *  - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call
+ *    synchronises the device and no call touches the legacy default stream unless the
+ *    caller passes it.
+ *  - Return value: HGC_OK or a negative HGC_ERR_* code.  Nothing throws, nothing prints.
+ *    Problems that only the device can see (an index outside its table, a bin outside the
+ *    grid, an iteration cap reached) set a status word in the workspace, which
+ *    hgc_workspace_status() reads back.
+ *  - Re-entrant: no global mutable state; concurrent calls need distinct workspaces.
+ *
+ * The paths named in the comments are relative to the cms-pepr/HGCalML repository.
+ */
+#ifndef HGCALML_B200_H
+#define HGCALML_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HGC_OK                     0
+#define HGC_ERR_INVALID_ARGUMENT  -1   /* shapes / attributes the reference op rejects too        */
+#define HGC_ERR_WORKSPACE         -2   /* workspace missing, misaligned or too small              */
+#define HGC_ERR_UNSUPPORTED       -3   /* valid for the reference, outside this library's limits  */
+#define HGC_ERR_CUDA              -4   /* a CUDA runtime call failed (see hgc_last_cuda_error)     */
+#define HGC_ERR_DEVICE_STATUS     -5   /* hgc_workspace_status found a non-zero device status word */
+
+/* Bits of the device status word. */
+#define HGC_STATUS_BIN_OUT_OF_RANGE    1u  /* a per-dimension bin index fell outside [0, n_bins)   */
+#define HGC_STATUS_FLAT_BIN_OVERFLOW   2u  /* a flat bin index was >= the number of bins           */
+#define HGC_STATUS_INDEX_OUT_OF_RANGE  4u  /* a gathered index was >= its table size               */
+#define HGC_STATUS_ITERATION_CAP       8u  /* an iterative kernel stopped at its iteration cap     */
+
+typedef void *hgc_stream_t; /* cudaStream_t */
+
+const char *hgc_strerror(int code);
+/* Text of the last CUDA error seen by the calling thread inside this library. */
+const char *hgc_last_cuda_error(void);
+/* Library version, major*10000 + minor*100 + patch. */
+int hgc_version(void);
+/* Number of kernels this library has launched in the calling process so far. */
+unsigned long long hgc_launch_count(void);
+
+/* Copies the status word of a workspace used by a previous call on `stream` to *status_out
+ * (host) and waits for that stream.  Returns HGC_ERR_DEVICE_STATUS when it is non-zero. */
+int hgc_workspace_status(const void *workspace, hgc_stream_t stream, unsigned *status_out);
+
+/* ---------------------------------------------------------------------------------------
+ * BinByCoordinates -- replaces BinByCoordinatesOpFunctor
+ * (modules/compiled/bin_by_coordinates_kernel.h:9-32, GPU body bin_by_coordinates_kernel.cu.cc:47-165).
+ * d_coords [n_vert, n_coords] (already shifted to >= 0), d_row_splits [n_rs], d_bin_width [1],
+ * d_n_bins [n_coords]; outputs d_assigned_bin [n_vert, n_coords+1] = [event, c_0 .. c_{n-1}],
+ * d_flat_assigned_bin [n_vert], d_n_per_bin [n_total_bins] (zeroed always, filled when
+ * calc_n_per_bin).  n_total_bins = prod(n_bins) * (n_rs-1), computed by the caller as the
+ * reference's NbinsHelper does (bin_by_coordinates_kernel.cc:17-35).
+ * ------------------------------------------------------------------------------------- */
+size_t hgc_bin_by_coordinates_workspace_bytes(int n_vert, int n_coords, int n_rs, int n_total_bins);
+int hgc_bin_by_coordinates(
+        const float *d_coords, const int *d_row_splits, const float *d_bin_width, const int *d_n_bins,
+        int *d_assigned_bin, int *d_flat_assigned_bin, int *d_n_per_bin,
+        int n_vert, int n_coords, int n_rs, int n_total_bins, int calc_n_per_bin,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * BinnedSelectKnn -- replaces BinnedSelectKnnOpFunctor
+ * (modules/compiled/binned_select_knn_kernel.h:8-38, GPU body binned_select_knn_kernel.cu.cc:80-288).
+ * All inputs in bin-sorted order: d_coord [n_vert, n_coords], d_bin_idx [n_vert],
+ * d_direction [n_vert] (read only when use_direction), d_dim_bin_idx [n_vert, n_bin_dim+1],
+ * d_bin_boundaries [n_bboundaries], d_n_bins [n_bin_dim], d_bin_width [1].
+ * Outputs d_indices / d_dist [n_vert, n_neigh]: slot 0 is the query itself, slots 1.. hold the
+ * n_neigh-1 nearest other hits of the same event in ascending (distance, index) order -- the
+ * reference leaves them in scan order; as a set the rows are identical -- padded with -1
+ * (or the query's own index when tf_compat) and distance 0.
+ * Limits: 2 <= n_bin_dim <= 5, 2 <= n_coords <= 16, 1 <= n_neigh <= 513.
+ * ------------------------------------------------------------------------------------- */
+size_t hgc_binned_select_knn_workspace_bytes(int n_vert, int n_neigh, int n_coords, int n_bin_dim);
+int hgc_binned_select_knn(
+        const float *d_coord, const int *d_bin_idx, const int *d_direction, const int *d_dim_bin_idx,
+        const int *d_bin_boundaries, const int *d_n_bins, const float *d_bin_width,
+        int *d_indices, float *d_dist,
+        int n_vert, int n_neigh, int n_coords, int n_bin_dim, int n_bboundaries,
+        int tf_compat, int use_direction,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * IndexReplacer -- replaces IndexReplacerOpFunctor (modules/compiled/index_replacer_kernel.h:8-20):
+ * replaced[i] = replacements[to_be_replaced[i]], negative entries pass through, entries beyond
+ * the table are left unwritten (and flagged in d_status when given; may be NULL).
+ * ------------------------------------------------------------------------------------- */
+int hgc_index_replacer(
+        const int *d_to_be_replaced, const int *d_replacements, int *d_replaced,
+        int n_to_be_replaced, int n_replacements, unsigned *d_status, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * AccumulateKnn -- replaces AccumulateKnnOpFunctor
+ * (modules/compiled/accumulate_knn_kernel.h:9-29, GPU body accumulate_knn_kernel.cu.cc:23-139).
+ * d_weights [n_vert, n_neigh] is the op's `distances` input, used verbatim as a weight;
+ * d_feat [n_vert, n_feat]; d_idxs [n_vert, n_neigh] (-1 = skip).  d_out_feat [n_vert, n_out_feat]
+ * with n_out_feat = 2*n_feat ([mean | max]) when mean_and_max, else n_feat; d_out_maxidxs
+ * [n_vert, n_feat] (written only when mean_and_max; may be NULL to skip it).
+ * No workspace.  Sums run over the slots in order, so the mean is bit-identical to the CPU op.
+ * ------------------------------------------------------------------------------------- */
+int hgc_accumulate_knn(
+        const float *d_weights, const float *d_feat, const int *d_idxs,
+        float *d_out_feat, int *d_out_maxidxs,
+        int n_vert, int n_neigh, int n_feat, int n_out_feat, int n_moments, int mean_and_max,
+        hgc_stream_t stream);
+
+/* Same op with the weighting of the Python wrapper fused in (modules/accknn_op.py:52):
+ * weight = exp(-(distance_scale * d_distances[v,k])), the product rounded to float32 first, so
+ * distance_scale = 10 on squared distances is GravNet's AccumulateKnn(10.*distsq, ..)
+ * (modules/GravNetLayersRagged.py:3269) and distance_scale = 1 is the wrapper as is.
+ * d_order (may be NULL) is a permutation of the hits giving the order in which rows are
+ * processed -- results do not depend on it, cache locality does. */
+int hgc_accumulate_knn_exp(
+        const float *d_distances, const float *d_feat, const int *d_idxs,
+        float *d_out_feat, int *d_out_maxidxs,
+        int n_vert, int n_neigh, int n_feat, int n_out_feat, int mean_and_max,
+        float distance_scale, const int *d_order, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * BinnedSelectKnn, wrapper level -- replaces the whole Python function BinnedSelectKnn
+ * (modules/binned_select_knn_op.py:32-95: BinByCoordinates + argsort + gathers + the op +
+ * IndexReplacer + scatter back) in one call with no host synchronisation.
+ * d_coords [n_vert, n_coords] and d_row_splits [n_rs] in the caller's order; outputs
+ * d_indices / d_dist [n_vert, n_neigh] in the caller's order and numbering.
+ * n_bins <= 0 selects the wrapper's default (binned_select_knn_op.py:59-63).
+ * d_sorting_out (may be NULL) receives the bin-sorting permutation [n_vert].
+ * ------------------------------------------------------------------------------------- */
+size_t hgc_binned_select_knn_ragged_workspace_bytes(int n_vert, int n_neigh, int n_coords, int n_rs,
+                                                    int n_bins, int max_bin_dims);
+int hgc_binned_select_knn_ragged(
+        const float *d_coords, const int *d_row_splits, const int *d_direction,
+        int *d_indices, float *d_dist, int *d_sorting_out,
+        int n_vert, int n_neigh, int n_coords, int n_rs,
+        int n_bins, int max_bin_dims, int tf_compat, int use_direction,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * BinnedAssignToCondensates -- replaces BinnedCondensatesFinderOpFunctor
+ * (modules/compiled/binned_assign_to_condensates_kernel.h:8-38; the reference has a CPU body
+ * only, binned_assign_to_condensates_kernel.cc:128-241).  Argument order and meaning as the
+ * functor's; all arrays in bin-sorted order, *_h are the high-beta subset.  Outputs:
+ * d_high_assigned_status_h [n_h] (1 for condensates), d_assignment [n_vert], d_association
+ * [n_vert], d_alpha_indices [n_h] (-1 padded per event), d_n_condensates [num_rows+1].
+ * ------------------------------------------------------------------------------------- */
+size_t hgc_binned_assign_to_condensates_workspace_bytes(int n_vert, int n_vert_h, int num_rows,
+                                                        int dimensions);
+int hgc_binned_assign_to_condensates(
+        int dimensions, int dimensions_binning,
+        const float *d_ccoords_h, const float *d_dist_h, const float *d_beta_h,
+        const int *d_no_condensation_mask_h,
+        int *d_high_assigned_status_h,
+        const int *d_original_indices_h, const int *d_row_splits_h,
+        const float *d_ccoords, const float *d_dist, const int *d_no_condensation_mask,
+        const int *d_indices_to_filtered,
+        int *d_assignment, int *d_association, int *d_n_condensates, int *d_alpha_indices,
+        const int *d_bin_splits, const int *d_n_bins, const float *d_bin_widths,
+        const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, int assign_by_max_beta,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HGCALML_B200_H */

@@ -1,0 +1,78 @@
+"""CPU suite: the C-ABI library loads without a GPU, exports every symbol the public header declares,
+and rejects malformed arguments on the host before touching the device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "hgcalml_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hgc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    from hgcalml_b200 import _capi
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(_capi.lib, n), f"{n} declared in include/hgcalml_b200.h but not exported"
+
+
+def test_error_strings_and_version():
+    from hgcalml_b200 import _capi
+    assert _capi.lib.hgc_version() >= 100
+    assert _capi.lib.hgc_strerror(0) == b"ok"
+    for code in (-1, -2, -3, -4, -5):
+        assert _capi.lib.hgc_strerror(code) not in (b"ok", b"unknown error code")
+
+
+def test_host_side_validation_needs_no_gpu():
+    from hgcalml_b200 import _capi
+    L = _capi.lib
+    nul = ctypes.c_void_p(None)
+    # op shape rules (binned_select_knn_kernel.cc:336-352): 2..5 binning dims, >= 2 coordinates
+    assert L.hgc_binned_select_knn(nul, nul, nul, nul, nul, nul, nul, nul, nul,
+                                   10, 4, 3, 1, 5, 0, 0, nul, 0, nul) == -1
+    assert L.hgc_binned_select_knn(nul, nul, nul, nul, nul, nul, nul, nul, nul,
+                                   10, 4, 3, 6, 5, 0, 0, nul, 0, nul) == -1
+    assert L.hgc_binned_select_knn(nul, nul, nul, nul, nul, nul, nul, nul, nul,
+                                   10, 4, 1, 3, 5, 0, 0, nul, 0, nul) == -1
+    # beyond the library's limits
+    assert L.hgc_binned_select_knn(nul, nul, nul, nul, nul, nul, nul, nul, nul,
+                                   10, 1000, 3, 3, 5, 0, 0, nul, 0, nul) == -3
+    # null tensors
+    assert L.hgc_binned_select_knn(nul, nul, nul, nul, nul, nul, nul, nul, nul,
+                                   10, 4, 3, 3, 5, 0, 0, nul, 0, nul) == -1
+    # AccumulateKnn: output width must be F or 2F
+    assert L.hgc_accumulate_knn(nul, nul, nul, nul, nul, 10, 4, 8, 9, 0, 1, nul) == -1
+    # empty inputs are fine and launch nothing
+    assert L.hgc_accumulate_knn(nul, nul, nul, nul, nul, 0, 4, 8, 16, 0, 1, nul) == 0
+    assert L.hgc_index_replacer(nul, nul, nul, 0, 0, nul, nul) == 0
+    # workspace queries are pure host arithmetic and grow with the problem
+    a = L.hgc_binned_select_knn_ragged_workspace_bytes(1000, 16, 4, 2, -1, 3)
+    b = L.hgc_binned_select_knn_ragged_workspace_bytes(100000, 16, 4, 2, -1, 3)
+    assert 0 < a < b
+    assert L.hgc_binned_select_knn_ragged_workspace_bytes(1000, 16, 12, 2, -1, 9) == 0
+
+
+def test_no_cpu_fallback_in_python_layer():
+    import torch
+    from hgcalml_b200 import _capi
+    from hgcalml_b200.accknn_op import AccumulateKnn
+    with pytest.raises(_capi.HgcError):
+        AccumulateKnn(torch.zeros(4, 2), torch.zeros(4, 4), torch.zeros(4, 2, dtype=torch.int32))
+
+
+def test_product_does_not_import_checker():
+    """Nothing under hgcalml_b200/ may import or load the CPU checker."""
+    pkg = os.path.join(ROOT, "hgcalml_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cc")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src, os.path.join(dirpath, f)

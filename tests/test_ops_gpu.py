@@ -1,0 +1,302 @@
+"""GPU parity tests: every entry of the C ABI against the CPU checker and the golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, bits, assert_knn_equal
+from hgcalml_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def T(a, dev):
+    return torch.as_tensor(np.ascontiguousarray(a), device=dev)
+
+
+def N(t):
+    return t.detach().cpu().numpy()
+
+
+# ------------------------------------------------------------------ BinByCoordinates
+def test_bin_by_coordinates_golden(cuda):
+    from hgcalml_b200.bin_by_coordinates_op import BinByCoordinates
+    g = load_golden("bin_by_coordinates")
+    binass, flat, nb, bw, nper = BinByCoordinates(T(g["coords"], cuda), T(g["row_splits"], cuda),
+                                                  n_bins=int(g["n_bins_arg"]))
+    assert np.array_equal(N(nb), g["n_bins"]) and np.array_equal(bits(N(bw)), bits(g["bin_width"]))
+    assert np.array_equal(N(binass), g["binass"])
+    assert np.array_equal(N(flat), g["flat"])
+    assert np.array_equal(N(nper), g["nper"])
+
+
+@pytest.mark.parametrize("dims,sizes", [(2, [300, 5000]), (3, [0, 20000, 17]), (4, [4000, 4000, 1]),
+                                        (5, [2500])])
+def test_bin_by_coordinates_vs_checker(cuda, oracle, dims, sizes):
+    from hgcalml_b200.bin_by_coordinates_op import BinByCoordinates
+    c, _, rs = synth.shower_batch(sizes, dims=dims, n_feat=1, seed=31 + dims)
+    for kw in (dict(n_bins=9), dict(bin_width=np.array([0.21], np.float32)), dict(n_bins=4, calc_n_per_bin=False)):
+        ref = oracle.BinByCoordinates(c, rs, **kw)
+        got = BinByCoordinates(T(c, cuda), T(rs, cuda), **kw)
+        for r, gt in zip(ref, got):
+            assert np.array_equal(np.asarray(r).view(np.int32), N(gt).view(np.int32)), kw
+
+
+# ------------------------------------------------------------------ BinnedSelectKnn (op level)
+def _sorted_inputs(oracle, K, c, rs, n_bins=None, max_bin_dims=3):
+    """Bin-sorted op inputs made by the checker's wrapper glue."""
+    mbd = min(max_bin_dims, c.shape[1])
+    if n_bins is None:
+        n_bins = oracle.default_n_bins(int(rs[1]), K, mbd)
+    dbin, binning, nb, bw, nper = oracle.BinByCoordinates(c[:, :mbd], rs, n_bins=n_bins)
+    sorting = np.argsort(binning, kind="stable")
+    bb = np.concatenate([[0], nper]).cumsum().astype(np.int32)
+    return c[sorting], binning[sorting], dbin[sorting], bb, nb, bw, sorting
+
+
+@pytest.mark.parametrize("K,dims,mbd,sizes", [
+    (16, 3, 3, [6000]), (24, 4, 3, [2500, 11, 0, 3000]), (8, 2, 2, [4000, 100]), (33, 4, 4, [3000, 40]),
+    (65, 5, 5, [1500, 1500]), (130, 4, 3, [2000]), (1, 3, 3, [500]), (2, 3, 2, [700]), (64, 8, 3, [2500]),
+])
+def test_binned_select_knn_op_vs_checker(cuda, oracle, K, dims, mbd, sizes):
+    from hgcalml_b200.binned_select_knn_op import _BinnedSelectKnn
+    c, _, rs = synth.shower_batch(sizes, dims=dims, n_feat=1, seed=17 * K + dims)
+    sc, sb, sdb, bb, nb, bw, _ = _sorted_inputs(oracle, K, c, rs, max_bin_dims=mbd)
+    ri, rd = oracle.op_binned_select_knn(K, sc, sb, sdb, bb, nb, bw)
+    gi, gd = _BinnedSelectKnn(K, T(sc, cuda), T(sb, cuda), T(sdb, cuda), T(bb, cuda), T(nb, cuda), T(bw, cuda))
+    ties = assert_knn_equal(N(gi), N(gd), ri, rd, what=f"K={K}")
+    assert ties <= max(2, len(c) // 200)
+    # rows come out in canonical order already
+    ci, cd = oracle.canonical_knn(N(gi), N(gd))
+    assert np.array_equal(ci, N(gi)) and np.array_equal(bits(cd), bits(N(gd)))
+
+
+def test_binned_select_knn_op_direction_and_tf_compat(cuda, oracle):
+    from hgcalml_b200.binned_select_knn_op import _BinnedSelectKnn
+    c, _, rs = synth.shower_batch([3000, 25, 2000], dims=4, n_feat=1, seed=91)
+    K = 12
+    sc, sb, sdb, bb, nb, bw, sorting = _sorted_inputs(oracle, K, c, rs)
+    direction = np.random.default_rng(4).integers(0, 4, len(c)).astype(np.int32)
+    for kw in (dict(direction=direction), dict(tf_compatible=True), dict(direction=direction, tf_compatible=True)):
+        ri, rd = oracle.op_binned_select_knn(K, sc, sb, sdb, bb, nb, bw, **kw)
+        tk = {k: (T(v, cuda) if k == "direction" else v) for k, v in kw.items()}
+        gi, gd = _BinnedSelectKnn(K, T(sc, cuda), T(sb, cuda), T(sdb, cuda), T(bb, cuda), T(nb, cuda),
+                                  T(bw, cuda), **tk)
+        if kw.get("tf_compatible"):
+            # padding repeats the query's own index; compare after mapping it back to -1
+            ri = np.where((ri == np.arange(len(c))[:, None]) & (np.arange(K)[None] > 0), -1, ri)
+            gi_n = N(gi)
+            gi_n = np.where((gi_n == np.arange(len(c))[:, None]) & (np.arange(K)[None] > 0), -1, gi_n)
+            assert_knn_equal(gi_n, N(gd), ri, rd, what=str(kw))
+        else:
+            assert_knn_equal(N(gi), N(gd), ri, rd, what=str(kw))
+
+
+# ------------------------------------------------------------------ BinnedSelectKnn (wrapper level)
+@pytest.mark.parametrize("name", ["knn_uniform3d", "knn_showers4d", "knn_showers4d_bin4",
+                                  "knn_showers4d_direction", "knn_showers4d_tfcompat"])
+def test_binned_select_knn_golden(cuda, name):
+    from hgcalml_b200.binned_select_knn_op import BinnedSelectKnn
+    g = load_golden(name)
+    kw = {}
+    if "n_bins" in g:
+        kw["n_bins"] = int(g["n_bins"])
+    if "max_bin_dims" in g:
+        kw["max_bin_dims"] = int(g["max_bin_dims"])
+    if "direction" in g:
+        kw["direction"] = T(g["direction"], cuda)
+    if "tf_compatible" in g:
+        kw["tf_compatible"] = bool(g["tf_compatible"])
+    K = int(g["K"])
+    gi, gd = BinnedSelectKnn(K, T(g["coords"], cuda), T(g["row_splits"], cuda), **kw)
+    gi, gd, ri = N(gi), N(gd), g["idx"]
+    if kw.get("tf_compatible"):
+        n = len(gi)
+        own = (np.arange(K)[None] > 0)
+        gi = np.where((gi == np.arange(n)[:, None]) & own, -1, gi)
+        ri = np.where((ri == np.arange(n)[:, None]) & own, -1, ri)
+    assert_knn_equal(gi, gd, ri, g["dist"], what=name)
+
+
+@pytest.mark.parametrize("K,dims,sizes,kw", [
+    (16, 3, [20000], dict(n_bins=10)),
+    (64, 4, [12000, 7000], dict()),
+    (32, 4, [9000, 3, 0, 4000], dict(max_bin_dims=4)),
+    (10, 6, [5000], dict(max_bin_dims=2)),
+])
+def test_binned_select_knn_wrapper_vs_checker(cuda, oracle, K, dims, sizes, kw):
+    from hgcalml_b200.binned_select_knn_op import BinnedSelectKnn
+    if dims == 3:
+        c, _, rs = synth.uniform_event(sizes[0], 3, 1, seed=101)
+    else:
+        c, _, rs = synth.shower_batch(sizes, dims=dims, n_feat=1, seed=5 + K)
+    ri, rd = oracle.BinnedSelectKnn(K, c, rs, **kw)
+    gi, gd, sorting = BinnedSelectKnn(K, T(c, cuda), T(rs, cuda), return_sorting=True, **kw)
+    ties = assert_knn_equal(N(gi), N(gd), ri, rd, what=f"K={K} {kw}")
+    assert ties <= 3
+    assert np.array_equal(np.sort(N(sorting)), np.arange(len(c)))
+    # run to run determinism
+    gi2, gd2 = BinnedSelectKnn(K, T(c, cuda), T(rs, cuda), **kw)
+    assert torch.equal(gi, gi2) and torch.equal(gd, gd2)
+
+
+def test_knn_exactness_brute_force_full_size(cuda, oracle):
+    """Size-independent property at the benchmark's event size: sampled rows equal the definitional
+    kNN (bit-identical distances), every row has the query first and ascending distances."""
+    from hgcalml_b200.binned_select_knn_op import BinnedSelectKnn
+    c, _, rs = synth.shower_batch([200000, 200000], dims=4, n_feat=1, seed=500, with_features=False)
+    K = 64
+    gi, gd = BinnedSelectKnn(K, T(c, cuda), T(rs, cuda))
+    gi, gd = N(gi), N(gd)
+    assert (gi[:, 0] == np.arange(len(c))).all() and (gd[:, 0] == 0).all()
+    assert (np.diff(gd[:, 1:], axis=1) >= 0).all()
+    assert (gi >= 0).all()
+    ev = np.searchsorted(rs, gi.ravel(), side="right") - 1
+    assert (ev.reshape(gi.shape) == ev.reshape(gi.shape)[:, :1]).all()  # neighbours stay inside the event
+    rows, bi, bd = oracle.brute_force_knn(K, c, rs, max_rows=400)
+    assert np.array_equal(bits(gd[rows]), bits(bd))
+    assert (gi[rows] == bi).mean() > 0.9999
+
+
+# ------------------------------------------------------------------ IndexReplacer
+def test_index_replacer(cuda, oracle):
+    from hgcalml_b200.index_replacer_op import IndexReplacer
+    rng = np.random.default_rng(0)
+    rep = rng.permutation(5000).astype(np.int32)
+    tbr = rng.integers(-1, 5000, (700, 9)).astype(np.int32)
+    assert np.array_equal(N(IndexReplacer(T(tbr, cuda), T(rep, cuda))), oracle.op_index_replacer(tbr, rep))
+
+
+# ------------------------------------------------------------------ AccumulateKnn
+@pytest.mark.parametrize("n,K,F,mm", [(5000, 16, 32, True), (3000, 64, 64, True), (2000, 64, 64, False),
+                                      (1500, 7, 16, True), (1000, 40, 128, True), (800, 9, 256, True),
+                                      (900, 12, 10, True), (700, 5, 3, False), (600, 33, 8, True)])
+def test_accumulate_knn_vs_checker(cuda, oracle, n, K, F, mm):
+    """Linear-weight op: bit-identical mean, max and arg-max (sums run in slot order)."""
+    from hgcalml_b200.accknn_op import AccumulateLinKnn
+    rng = np.random.default_rng(n + K + F)
+    feat = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.random((n, K), dtype=np.float32)
+    idx = rng.integers(0, n, (n, K)).astype(np.int32)
+    idx[:, 0] = np.arange(n)
+    pad = rng.integers(1, K + 1, n)
+    idx[np.arange(K)[None] >= pad[:, None]] = -1          # trailing -1 padding
+    idx[::97, 0] = -1                                      # rows whose first slot is invalid
+    ro, ra = oracle.op_accumulate_knn(w, feat, idx, mean_and_max=mm)
+    go, ga = AccumulateLinKnn(T(w, cuda), T(feat, cuda), T(idx, cuda), mean_and_max=mm)
+    assert np.array_equal(bits(N(go)), bits(ro))
+    if mm:
+        assert np.array_equal(N(ga), ra)
+
+
+@pytest.mark.parametrize("name", ["knn_uniform3d", "knn_showers4d"])
+def test_accumulate_knn_exp_golden(cuda, name):
+    """exp(-10 d^2)-weighted op against the reference's outputs: 1e-5 relative on the features (the
+    weight comes from expf on the device vs float32 exp on the host), max bit-exact where unique."""
+    from hgcalml_b200.accknn_op import AccumulateKnn
+    g = load_golden(name)
+    d = np.float32(10.) * g["dist"]
+    go, ga = AccumulateKnn(T(d, cuda), T(g["feats"], cuda), T(g["idx"], cuda))
+    go = N(go)
+    scale = np.maximum(np.abs(g["acc"]), 1e-3)
+    assert (np.abs(go - g["acc"]) <= 1e-5 * scale).all()
+    assert (N(ga) == g["maxidx"]).mean() > 0.999
+
+
+def test_accumulate_knn_order_is_only_a_schedule(cuda):
+    from hgcalml_b200.accknn_op import AccumulateKnn
+    rng = np.random.default_rng(3)
+    n, K, F = 4000, 32, 64
+    feat = T(rng.standard_normal((n, F), dtype=np.float32), cuda)
+    d = T(rng.random((n, K), dtype=np.float32), cuda)
+    idx = T(rng.integers(0, n, (n, K)).astype(np.int32), cuda)
+    order = T(rng.permutation(n).astype(np.int32), cuda)
+    a = AccumulateKnn(d, feat, idx)
+    b = AccumulateKnn(d, feat, idx, order=order)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_accumulate_linearity_full_size(cuda):
+    """Size-independent property at the benchmark's event size: the mean half is linear in the
+    features (checked against float64 sums of a sample), the max half is the max of the products."""
+    from hgcalml_b200.accknn_op import AccumulateLinKnn
+    rng = np.random.default_rng(8)
+    n, K, F = 200000, 64, 64
+    feat = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.random((n, K), dtype=np.float32)
+    idx = rng.integers(0, n, (n, K)).astype(np.int32)
+    go, ga = AccumulateLinKnn(T(w, cuda), T(feat, cuda), T(idx, cuda))
+    go, ga = N(go), N(ga)
+    rows = rng.choice(n, 300, replace=False)
+    prod = feat[idx[rows]].astype(np.float64) * w[rows][:, :, None]
+    assert np.allclose(go[rows, :F], prod.mean(axis=1), rtol=1e-5, atol=1e-6)
+    assert np.array_equal(go[rows, F:], (feat[idx[rows]] * w[rows][:, :, None]).max(axis=1))
+    picked = np.take_along_axis(feat[ga[rows]], np.arange(F)[None, :, None], axis=2)[:, :, 0]
+    assert picked.shape == (300, F)
+
+
+# ------------------------------------------------------------------ BinnedAssignToCondensates
+COND_KEYS = ("assignment", "association", "alpha_idx", "is_cond", "n_condensates")
+
+
+@pytest.mark.parametrize("name", [f"cond_{t}_{m}" for t in ("const", "var", "masked", "maskedheavy")
+                                  for m in ("maxbeta", "mindist")])
+def test_condensates_golden(cuda, name):
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    g = load_golden(name)
+    out = BuildAndAssignCondensatesBinned(T(g["ccoords"], cuda), T(g["betas"], cuda), T(g["dist"], cuda),
+                                          T(g["row_splits"], cuda), float(g["beta_threshold"]),
+                                          no_condensation_mask=T(g["mask"], cuda),
+                                          assign_by_max_beta=bool(g["assign_by_max_beta"]))
+    for got, key in zip(out, COND_KEYS):
+        assert np.array_equal(N(got), g[key]), key
+
+
+@pytest.mark.parametrize("amb", [True, False])
+def test_condensates_vs_checker_midsize(cuda, oracle, amb):
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    cc, beta, rs = synth.condensation_batch(3, 30000, 120, 3, 0.1, seed=410)
+    d = np.full_like(beta, 0.5)
+    ref = oracle.BuildAndAssignCondensatesBinned(cc, beta, d, rs, 0.1, assign_by_max_beta=amb)
+    got = BuildAndAssignCondensatesBinned(T(cc, cuda), T(beta, cuda), T(d, cuda), T(rs, cuda), 0.1,
+                                          assign_by_max_beta=amb)
+    for r, gt, key in zip(ref, got, COND_KEYS):
+        assert np.array_equal(N(gt), r), key
+
+
+def test_condensates_degenerate_inputs(cuda, oracle):
+    """All hits at one point and an event without any high-beta hit (the reference's unit test uses
+    all-zero coordinates, tests/unit/condensate.py:45-46)."""
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    rng = np.random.default_rng(1)
+    cc = np.zeros((600, 3), np.float32)
+    beta = rng.random((600, 1), dtype=np.float32)
+    beta[300:] *= 0.05
+    rs = np.array([0, 300, 600], np.int32)
+    d = np.full_like(beta, 0.3)
+    for amb in (True, False):
+        ref = oracle.BuildAndAssignCondensatesBinned(cc, beta, d, rs, 0.1, assign_by_max_beta=amb)
+        got = BuildAndAssignCondensatesBinned(T(cc, cuda), T(beta, cuda), T(d, cuda), T(rs, cuda), 0.1,
+                                              assign_by_max_beta=amb)
+        for r, gt, key in zip(ref, got, COND_KEYS):
+            assert np.array_equal(N(gt), r), key
+
+
+def test_condensates_full_size_invariants(cuda):
+    """Benchmark-size run (4 x 200k hits): structural invariants of the reference's own unit test."""
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    cc, beta, rs = synth.condensation_batch(4, 200000, 500, 3, 0.1, seed=400)
+    d = np.full_like(beta, 0.5)
+    a, asso, alpha, is_cond, ncond = (N(x) for x in BuildAndAssignCondensatesBinned(
+        T(cc, cuda), T(beta, cuda), T(d, cuda), T(rs, cuda), 0.1, assign_by_max_beta=True))
+    assert is_cond.sum() == len(alpha) == ncond[-1]
+    for e in range(4):
+        al = alpha[ncond[e]:ncond[e + 1]]
+        assert np.array_equal(a[al, 0], np.arange(len(al)))
+        assert np.array_equal(asso[al], al)
+        assert ((al >= rs[e]) & (al < rs[e + 1])).all()
+        assert (np.diff(beta[al, 0]) <= 0).all()  # condensates come in descending beta
+    assert ((a[:, 0] < 0) == (asso < 0)).all()
+    # every assigned hit lies inside its condensate's radius
+    ok = asso >= 0
+    dd = ((cc[ok] - cc[asso[ok]]) ** 2).sum(axis=1)
+    assert (dd <= 0.25 * (1 + 1e-5)).all()
