@@ -1,0 +1,244 @@
+// TensorFlow custom-op shims: the registered ops of HGCalML's GravNet / object-condensation
+// inference path, forwarding to the C ABI of libhgcalml_b200.so.
+//
+// Each shim keeps the reference's op name, attributes, input/output order and dtypes
+// (modules/compiled/{bin_by_coordinates,binned_select_knn,index_replacer,accumulate_knn,
+// binned_assign_to_condensates}_module.cc), so the unchanged Python wrappers load it with
+// tf.load_op_library.  A shim does shape checks, allocate_output / allocate_temp, and ONE call
+// into the library on the op's own CUDA stream; it never synchronises the device.
+//
+// Build (needs a TensorFlow installation):
+//   g++ -std=c++17 -shared -fPIC hgc_tf_ops.cc -o hgc_tf_ops.so \
+//       $(python -c 'import tensorflow as tf; print(" ".join(tf.sysconfig.get_compile_flags()))') \
+//       -I../../include -L.. -lhgcalml_b200 \
+//       $(python -c 'import tensorflow as tf; print(" ".join(tf.sysconfig.get_link_flags()))')
+#define EIGEN_USE_GPU
+#include "tensorflow/core/framework/op.h"
+#include "tensorflow/core/framework/op_kernel.h"
+#include "tensorflow/core/framework/shape_inference.h"
+
+#include "hgcalml_b200.h"
+
+namespace tensorflow {
+namespace {
+
+typedef Eigen::GpuDevice GPUDevice;
+
+inline hgc_stream_t StreamOf(OpKernelContext *ctx) {
+    return static_cast<hgc_stream_t>(ctx->eigen_device<GPUDevice>().stream());
+}
+
+inline Status FromHgc(int rc, const char *op) {
+    if (rc == HGC_OK) return OkStatus();
+    if (rc == HGC_ERR_INVALID_ARGUMENT || rc == HGC_ERR_UNSUPPORTED)
+        return errors::InvalidArgument(op, ": ", hgc_strerror(rc));
+    return errors::Internal(op, ": ", hgc_strerror(rc), " ", hgc_last_cuda_error());
+}
+
+// Scratch memory comes from TensorFlow's allocator (uint8 temp tensor; TF aligns to 64 bytes, the
+// library wants 256, so over-allocate and round the pointer up).
+struct Workspace {
+    Tensor t;
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    Status Allocate(OpKernelContext *ctx, size_t need) {
+        TF_RETURN_IF_ERROR(ctx->allocate_temp(DT_UINT8, TensorShape({(int64_t)need + 256}), &t));
+        uintptr_t p = reinterpret_cast<uintptr_t>(t.flat<uint8>().data());
+        ptr = reinterpret_cast<void *>((p + 255) / 256 * 256);
+        bytes = need;
+        return OkStatus();
+    }
+};
+
+// ------------------------------------------------------------------ BinByCoordinates
+// nbins (and bin_width) are pinned to host memory: the third output is sized from nbins, which the
+// reference reads back with a blocking cudaMemcpy (bin_by_coordinates_kernel.cu.cc:28-34).
+class BinByCoordinatesGpuOp : public OpKernel {
+public:
+    explicit BinByCoordinatesGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("calc_n_per_bin", &calc_n_per_bin_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &coords = ctx->input(0), &rs = ctx->input(1), &bw = ctx->input(2), &nbins = ctx->input(3);
+        const int n_vert = coords.dim_size(0), n_coords = coords.dim_size(1), n_rs = rs.dim_size(0);
+        OP_REQUIRES(ctx, bw.dim_size(0) == 1,
+                    errors::InvalidArgument("BinByCoordinatesOp expects singleton (dim: 1) for bin width."));
+        OP_REQUIRES(ctx, nbins.dim_size(0) == n_coords,
+                    errors::InvalidArgument("BinByCoordinatesOp expects coordinate dimension for number of bins."));
+        int total = n_rs - 1;
+        for (int i = 0; i < n_coords; i++) total *= nbins.flat<int>()(i);  // host memory
+        Tensor *assigned, *flat, *nper;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, n_coords + 1}, &assigned));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert}, &flat));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(2, {total}, &nper));
+        // the kernels read nbins / bin_width on the device: stage the few host values in a temp
+        Tensor dev_params;
+        OP_REQUIRES_OK(ctx, ctx->allocate_temp(DT_INT32, {n_coords + 1}, &dev_params));
+        int *d_nbins = dev_params.flat<int>().data();
+        float *d_bw = reinterpret_cast<float *>(d_nbins + n_coords);
+        auto stream = ctx->eigen_device<GPUDevice>().stream();
+        cudaMemcpyAsync(d_nbins, nbins.flat<int>().data(), sizeof(int) * n_coords, cudaMemcpyHostToDevice, stream);
+        cudaMemcpyAsync(d_bw, bw.flat<float>().data(), sizeof(float), cudaMemcpyHostToDevice, stream);
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_bin_by_coordinates_workspace_bytes(n_vert, n_coords, n_rs, total)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_bin_by_coordinates(
+            coords.flat<float>().data(), rs.flat<int>().data(), d_bw, d_nbins,
+            assigned->flat<int>().data(), flat->flat<int>().data(), nper->flat<int>().data(),
+            n_vert, n_coords, n_rs, total, calc_n_per_bin_, ws.ptr, ws.bytes, StreamOf(ctx)), "BinByCoordinates"));
+    }
+private:
+    bool calc_n_per_bin_;
+};
+
+// ------------------------------------------------------------------ BinnedSelectKnn
+class BinnedSelectKnnGpuOp : public OpKernel {
+public:
+    explicit BinnedSelectKnnGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("n_neighbours", &K_));
+        OP_REQUIRES_OK(c, c->GetAttr("tf_compatible", &tf_compat_));
+        OP_REQUIRES_OK(c, c->GetAttr("use_direction", &use_direction_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &coords = ctx->input(0), &bin_idx = ctx->input(1), &dim_bin_idx = ctx->input(2),
+                     &bounds = ctx->input(3), &n_bins = ctx->input(4), &bw = ctx->input(5), &dir = ctx->input(6);
+        const int n_vert = coords.dim_size(0), n_coords = coords.dim_size(1);
+        const int n_bb = bounds.dim_size(0), n_bin_dims = n_bins.dim_size(0);
+        OP_REQUIRES(ctx, n_bin_dims > 1, errors::InvalidArgument("BinnedSelectKnnOp expects at least 2 binning dimensions."));
+        OP_REQUIRES(ctx, n_bin_dims < 6, errors::InvalidArgument("BinnedSelectKnnOp expects maximum 5 binning dimensions."));
+        OP_REQUIRES(ctx, dim_bin_idx.dim_size(1) - 1 == n_bin_dims,
+                    errors::InvalidArgument("BinnedSelectKnnOp expects number of bin dimensions (including row splits) -1 == number of total bin dimensions."));
+        OP_REQUIRES(ctx, n_coords > 1, errors::InvalidArgument("BinnedSelectKnnOp expects at least 2 dimensions."));
+        OP_REQUIRES(ctx, n_vert == bin_idx.dim_size(0),
+                    errors::InvalidArgument("BinnedSelectKnnOp expects same first dimension for bin idx and coordinates."));
+        OP_REQUIRES(ctx, bw.dim_size(0) == 1, errors::InvalidArgument("BinnedSelectKnnOp expects singleton (dim(1)) for bin width."));
+        if (use_direction_)
+            OP_REQUIRES(ctx, dir.dim_size(0) == n_vert,
+                        errors::InvalidArgument("BinnedSelectKnnOp needs a direction tensor with length nvert if use_direction=True."));
+        Tensor *idx, *dist;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, K_}, &idx));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, K_}, &dist));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_binned_select_knn_workspace_bytes(n_vert, K_, n_coords, n_bin_dims)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_binned_select_knn(
+            coords.flat<float>().data(), bin_idx.flat<int>().data(), dir.flat<int>().data(),
+            dim_bin_idx.flat<int>().data(), bounds.flat<int>().data(), n_bins.flat<int>().data(),
+            bw.flat<float>().data(), idx->flat<int>().data(), dist->flat<float>().data(),
+            n_vert, K_, n_coords, n_bin_dims, n_bb, tf_compat_, use_direction_, ws.ptr, ws.bytes, StreamOf(ctx)),
+            "BinnedSelectKnn"));
+    }
+private:
+    int K_;
+    bool tf_compat_, use_direction_;
+};
+
+// ------------------------------------------------------------------ IndexReplacer
+class IndexReplacerGpuOp : public OpKernel {
+public:
+    explicit IndexReplacerGpuOp(OpKernelConstruction *c) : OpKernel(c) {}
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &tbr = ctx->input(0), &rep = ctx->input(1);
+        Tensor *out;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, tbr.shape(), &out));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_index_replacer(tbr.flat<int>().data(), rep.flat<int>().data(),
+                                                       out->flat<int>().data(), tbr.NumElements(), rep.dim_size(0),
+                                                       nullptr, StreamOf(ctx)), "IndexReplacer"));
+    }
+};
+
+// ------------------------------------------------------------------ AccumulateKnn
+class AccumulateKnnGpuOp : public OpKernel {
+public:
+    explicit AccumulateKnnGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("n_moments", &n_moments_));
+        OP_REQUIRES_OK(c, c->GetAttr("mean_and_max", &mean_and_max_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &w = ctx->input(0), &feat = ctx->input(1), &idx = ctx->input(2);
+        const int n_vert = w.dim_size(0), K = idx.dim_size(1), F = feat.dim_size(1);
+        OP_REQUIRES(ctx, n_vert == idx.dim_size(0) && n_vert == feat.dim_size(0),
+                    errors::InvalidArgument("AccumulateKnnOp expects first dimensions of all inputs to match."));
+        OP_REQUIRES(ctx, K == w.dim_size(1),
+                    errors::InvalidArgument("AccumulateKnnOp expects second dimension of distance and neighbour index tensor to match"));
+        const int n_out = mean_and_max_ ? 2 * F : F;
+        Tensor *out, *maxidx;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, n_out}, &out));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, F}, &maxidx));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_accumulate_knn(
+            w.flat<float>().data(), feat.flat<float>().data(), idx.flat<int>().data(),
+            out->flat<float>().data(), maxidx->flat<int>().data(), n_vert, K, F, n_out, n_moments_,
+            mean_and_max_, StreamOf(ctx)), "AccumulateKnn"));
+    }
+private:
+    int n_moments_;
+    bool mean_and_max_;
+};
+
+// ------------------------------------------------------------------ BinnedAssignToCondensates
+// The reference registers a CPU kernel only and its wrapper pins the op to '/cpu'
+// (modules/assign_condensate_op.py:299); this GPU kernel is picked once that pin is removed.
+class BinnedAssignToCondensatesGpuOp : public OpKernel {
+public:
+    explicit BinnedAssignToCondensatesGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("beta_threshold", &beta_threshold_));
+        OP_REQUIRES_OK(c, c->GetAttr("assign_by_max_beta", &assign_by_max_beta_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &cc = ctx->input(0), &dist = ctx->input(1), &mask = ctx->input(3), &bin_splits = ctx->input(5),
+                     &itf = ctx->input(6), &orig = ctx->input(7), &rs = ctx->input(8), &n_bins = ctx->input(9),
+                     &bw = ctx->input(10), &cc_h = ctx->input(11), &dist_h = ctx->input(12), &beta_h = ctx->input(13),
+                     &mask_h = ctx->input(14), &rs_h = ctx->input(15);
+        const int n = cc.dim_size(0), n_h = beta_h.dim_size(0), dims = cc.dim_size(1);
+        const int dims_binning = n_bins.dim_size(0), num_rows = rs.dim_size(0) - 1;
+        Tensor *assigned_h, *assigned, *alpha, *asso, *ncond;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_h}, &assigned_h));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n}, &assigned));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(2, {n_h}, &alpha));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(3, {n}, &asso));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(4, {num_rows + 1}, &ncond));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_binned_assign_to_condensates_workspace_bytes(n, n_h, num_rows, dims)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_binned_assign_to_condensates(
+            dims, dims_binning, cc_h.flat<float>().data(), dist_h.flat<float>().data(), beta_h.flat<float>().data(),
+            mask_h.flat<int>().data(), assigned_h->flat<int>().data(), orig.flat<int>().data(),
+            rs_h.flat<int>().data(), cc.flat<float>().data(), dist.flat<float>().data(), mask.flat<int>().data(),
+            itf.flat<int>().data(), assigned->flat<int>().data(), asso->flat<int>().data(),
+            ncond->flat<int>().data(), alpha->flat<int>().data(), bin_splits.flat<int>().data(),
+            n_bins.flat<int>().data(), bw.flat<float>().data(), rs.flat<int>().data(), num_rows, n, n_h,
+            assign_by_max_beta_, ws.ptr, ws.bytes, StreamOf(ctx)), "BinnedAssignToCondensates"));
+    }
+private:
+    float beta_threshold_;
+    bool assign_by_max_beta_;
+};
+
+}  // namespace
+
+// Op signatures: identical to the reference's *_module.cc files.
+REGISTER_OP("BinByCoordinates").Attr("calc_n_per_bin: bool")
+    .Input("coordinates: float").Input("row_splits: int32").Input("bin_width: float").Input("nbins: int32")
+    .Output("bin_assignment: int32").Output("flat_bin_assignment: int32").Output("nperbin: int32");
+REGISTER_OP("BinnedSelectKnn").Attr("n_neighbours: int").Attr("tf_compatible: bool").Attr("use_direction: bool")
+    .Input("coords: float").Input("bin_idx: int32").Input("dim_bin_idx: int32").Input("bin_boundaries: int32")
+    .Input("n_bins: int32").Input("bin_width: float").Input("direction: int32")
+    .Output("indices: int32").Output("distances: float32");
+REGISTER_OP("IndexReplacer").Input("to_be_replaced: int32").Input("replacements: int32").Output("output: int32");
+REGISTER_OP("AccumulateKnn").Attr("n_moments: int").Attr("mean_and_max: bool")
+    .Input("distances: float32").Input("features: float32").Input("indices: int32")
+    .Output("out_features: float32").Output("out_max_idxs: int32");
+REGISTER_OP("BinnedAssignToCondensates").Attr("beta_threshold: float").Attr("assign_by_max_beta: bool")
+    .Input("ccoords: float32").Input("dist: float32").Input("beta: float32").Input("no_condensation_mask: int32")
+    .Input("bins_flat: int32").Input("bin_splits: int32").Input("indices_to_filtered: int32")
+    .Input("original_indices: int32").Input("row_splits: int32").Input("n_bins: int32").Input("bin_widths: float32")
+    .Input("ccoords_h: float32").Input("dist_h: float32").Input("beta_h: float32")
+    .Input("no_condensation_mask_h: int32").Input("row_splits_h: int32")
+    .Output("assigned_h: int32").Output("assigned: int32").Output("alpha_indices: int32")
+    .Output("association: int32").Output("n_condensates: int32");
+
+REGISTER_KERNEL_BUILDER(Name("BinByCoordinates").Device(DEVICE_GPU).HostMemory("nbins").HostMemory("bin_width"),
+                        BinByCoordinatesGpuOp);
+REGISTER_KERNEL_BUILDER(Name("BinnedSelectKnn").Device(DEVICE_GPU), BinnedSelectKnnGpuOp);
+REGISTER_KERNEL_BUILDER(Name("IndexReplacer").Device(DEVICE_GPU), IndexReplacerGpuOp);
+REGISTER_KERNEL_BUILDER(Name("AccumulateKnn").Device(DEVICE_GPU), AccumulateKnnGpuOp);
+REGISTER_KERNEL_BUILDER(Name("BinnedAssignToCondensates").Device(DEVICE_GPU), BinnedAssignToCondensatesGpuOp);
+
+}  // namespace tensorflow
