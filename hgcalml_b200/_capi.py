@@ -40,6 +40,7 @@ def _load():
         "hgc_bin_by_coordinates": (I, [P, P, P, P, P, P, P, I, I, I, I, I, P, S, P]),
         "hgc_binned_select_knn_workspace_bytes": (S, [I, I, I, I]),
         "hgc_binned_select_knn": (I, [P] * 9 + [I] * 7 + [P, S, P]),
+        "hgc_binned_select_knn_static": (I, [P] * 9 + [I] * 7 + [P]),
         "hgc_index_replacer": (I, [P, P, P, I, I, P, P]),
         "hgc_accumulate_knn": (I, [P] * 5 + [I] * 6 + [P]),
         "hgc_accumulate_knn_exp": (I, [P] * 5 + [I] * 5 + [ctypes.c_float, P, P]),

@@ -41,6 +41,7 @@ extern "C" const char *hgc_strerror(int code)
         case HGC_ERR_UNSUPPORTED: return "outside the limits of this library";
         case HGC_ERR_CUDA: return "CUDA runtime error";
         case HGC_ERR_DEVICE_STATUS: return "device status word is non-zero";
+        case HGC_ERR_STATIC_SCRATCH_TOO_SMALL: return "problem exceeds the built-in scratch of this entry point";
     }
     return "unknown error code";
 }

@@ -33,6 +33,7 @@ extern "C" {
 #define HGC_ERR_UNSUPPORTED       -3   /* valid for the reference, outside this library's limits  */
 #define HGC_ERR_CUDA              -4   /* a CUDA runtime call failed (see hgc_last_cuda_error)     */
 #define HGC_ERR_DEVICE_STATUS     -5   /* hgc_workspace_status found a non-zero device status word */
+#define HGC_ERR_STATIC_SCRATCH_TOO_SMALL -6 /* problem larger than the built-in scratch of a *_static entry */
 
 /* Bits of the device status word. */
 #define HGC_STATUS_BIN_OUT_OF_RANGE    1u  /* a per-dimension bin index fell outside [0, n_bins)   */
@@ -90,6 +91,36 @@ int hgc_binned_select_knn(
         int n_vert, int n_neigh, int n_coords, int n_bin_dim, int n_bboundaries,
         int tf_compat, int use_direction,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * BinnedSelectKnn for callers that cannot hand over device memory.  (No counterpart in the
+ * reference: there TensorFlow's allocator is always at hand.)
+ *
+ * Some users of this ABI have no way to obtain a workspace: a plain C or Fortran reconstruction
+ * job that links the library directly and owns no device allocator, or a serving process whose
+ * framework has claimed the GPU's memory up front, so that a cudaMalloc from inside the op either
+ * fails or is forbidden by the deployment's rules.  For them this entry takes the same arguments
+ * as hgc_binned_select_knn minus the workspace and computes the same result, keeping its scratch
+ * (a status word and the packed coordinates) in a fixed array that is part of the library's device
+ * image: 4 MiB + 256 bytes on every GPU that loads the library, held until the process exits.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Limits: n_vert <= HGC_STATIC_KNN_MAX_VERT and n_coords <= HGC_STATIC_KNN_MAX_COORDS, otherwise
+ * HGC_ERR_STATIC_SCRATCH_TOO_SMALL is returned and nothing is launched.
+ * First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) and remembers it; make that first call outside any stream capture.
+ * Sharing: all calls on one device use the same array, which still holds the previous call's
+ * data; the entry rewrites what it reads and clears the status word itself, but two calls that
+ * overlap on the GPU (different streams, or different host threads) race on it -- serialise them.
+ * ------------------------------------------------------------------------------------- */
+#define HGC_STATIC_KNN_MAX_VERT   262144
+#define HGC_STATIC_KNN_MAX_COORDS 4
+int hgc_binned_select_knn_static(
+        const float *d_coord, const int *d_bin_idx, const int *d_direction, const int *d_dim_bin_idx,
+        const int *d_bin_boundaries, const int *d_n_bins, const float *d_bin_width,
+        int *d_indices, float *d_dist,
+        int n_vert, int n_neigh, int n_coords, int n_bin_dim, int n_bboundaries,
+        int tf_compat, int use_direction, hgc_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * IndexReplacer -- replaces IndexReplacerOpFunctor (modules/compiled/index_replacer_kernel.h:8-20):
