@@ -16,10 +16,14 @@ __global__ void bin_keys_kernel(const float *__restrict__ coords, int coord_stri
                                 const float *__restrict__ bin_width, const int *__restrict__ n_bins,
                                 int *__restrict__ assigned, int *__restrict__ flat_out,
                                 int *__restrict__ sort_keys, int n_vert, int n_total_bins,
-                                const int *__restrict__ n_total_bins_dev, unsigned *status)
+                                const int *__restrict__ n_total_bins_dev, unsigned *status,
+                                const GridParams *__restrict__ grid, int n_all, int *__restrict__ sub_keys)
 {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert) return;
+    unsigned frac[kMaxBinDims];  // position inside the cell as a 16-bit fraction (ordering code only)
+#pragma unroll
+    for (int c = 0; c < kMaxBinDims; c++) frac[c] = 0u;
     const float bw = bin_width[0];
     const int total = n_total_bins_dev ? n_total_bins_dev[0] : n_total_bins;
     int stride = 1, flat = 0;
@@ -28,6 +32,12 @@ __global__ void bin_keys_kernel(const float *__restrict__ coords, int coord_stri
         if (shift) x = __fsub_rn(x, shift[c]);
         int ci = __float2int_rz(__fdiv_rn(x, bw));
         const int nb = n_bins[c];
+        if (sub_keys) {
+            const float u = __fdiv_rn(x, bw) - (float)ci;
+#pragma unroll
+            for (int k = 0; k < kMaxBinDims; k++)
+                if (k == c) frac[k] = (unsigned)fminf(fmaxf(u * 65536.f, 0.f), 65535.f);
+        }
         if (ci < 0 || ci >= nb) {
             ci = 0;
             flag_status(status, HGC_STATUS_BIN_OUT_OF_RANGE);
@@ -52,6 +62,26 @@ __global__ void bin_keys_kernel(const float *__restrict__ coords, int coord_stri
     if (assigned) assigned[(size_t)v * (n_dims + 1)] = event;
     if (flat_out) flat_out[v] = flat;
     if (sort_keys) sort_keys[v] = flat;
+    if (sub_keys) {
+#pragma unroll
+        for (int c = 0; c < kMaxBinDims; c++)
+            if (c >= n_dims && c < n_all) {
+                const float ext = grid->all_ext[c];
+                const float u = ext > 0.f ? (coords[(size_t)v * coord_stride + c] - grid->all_min[c]) / ext : 0.f;
+                frac[c] = (unsigned)fminf(fmaxf(u * 65536.f, 0.f), 65535.f);
+            }
+        unsigned code = 0u;
+#pragma unroll
+        for (int k = 0; k < kSubBits; k++) {
+            const int c = grid->sub_seq[k];
+            unsigned f = 0u;
+#pragma unroll
+            for (int q = 0; q < kMaxBinDims; q++)
+                if (q == c) { f = frac[q]; frac[q] = (frac[q] << 1) & 0xffffu; }
+            code = (code << 1) | (f >> 15);
+        }
+        sub_keys[v] = (int)code;
+    }
 }
 
 __global__ void adjacent_difference_kernel(const int *__restrict__ bounds, int *__restrict__ out, int n)
@@ -102,13 +132,13 @@ range_partial_kernel(const float *__restrict__ coords, int coord_stride, int n_d
 // One block: finishes the min/max reduction and derives the grid exactly as the Python wrappers do
 // (modules/bin_by_coordinates_op.py:49-71, modules/binned_select_knn_op.py:57-63), in float32.
 __global__ void __launch_bounds__(32)
-grid_setup_kernel(const float *__restrict__ partial, int n_partials, int n_dims,
+grid_setup_kernel(const float *__restrict__ partial, int n_partials, int n_dims, int n_all,
                   const int *__restrict__ row_splits, int n_rs, int n_bins_arg, int n_neigh,
                   int pre_normalized, GridParams *__restrict__ g)
 {
     const int c = threadIdx.x;
     float mn = 0.f, mx = 0.f;
-    if (c < n_dims) {
+    if (c < n_all) {
         mn = INFINITY; mx = -INFINITY;
         for (int p = 0; p < n_partials; p++) {
             mn = fminf(mn, partial[((size_t)p * 2 + 0) * kMaxBinDims + c]);
@@ -145,16 +175,38 @@ grid_setup_kernel(const float *__restrict__ partial, int n_partials, int n_dims,
         g->bins_per_event = prod;
         g->n_total_bins = prod * (n_rs - 1);
     }
+    // within-bin ordering code: start from the bin width (binned) or the batch range (others)
+    float ext = 0.f;
+    if (c < n_dims) ext = bw;
+    else if (c < n_all) { ext = mx - mn; if (!isfinite(ext)) ext = 0.f; }
+    if (c < kMaxBinDims) { g->all_min[c] = mn; g->all_ext[c] = ext; }
+    float cell[kMaxBinDims];
+#pragma unroll
+    for (int k = 0; k < kMaxBinDims; k++) cell[k] = __shfl_sync(0xffffffffu, ext, k);
+    if (c == 0) {
+        for (int k = 0; k < kSubBits; k++) {
+            int best = 0;
+#pragma unroll
+            for (int q = 1; q < kMaxBinDims; q++)
+                if (cell[q] > cell[best]) best = q;
+            g->sub_seq[k] = best;
+#pragma unroll
+            for (int q = 0; q < kMaxBinDims; q++)
+                if (q == best) cell[q] *= 0.5f;
+        }
+    }
 }
 
-int compute_grid(const float *coords, int coord_stride, int n_dims, int n_vert,
+int compute_grid(const float *coords, int coord_stride, int n_dims, int n_all, int n_vert,
                  const int *row_splits, int n_rs, int n_bins_arg, int n_neigh, int pre_normalized,
                  float *partial, GridParams *grid, cudaStream_t stream)
 {
+    if (n_all < n_dims) n_all = n_dims;
+    if (n_all > kMaxBinDims) n_all = kMaxBinDims;
     const int blocks = range_partial_blocks(n_vert);
-    range_partial_kernel<<<blocks, 256, 0, stream>>>(coords, coord_stride, n_dims, n_vert, partial);
+    range_partial_kernel<<<blocks, 256, 0, stream>>>(coords, coord_stride, n_all, n_vert, partial);
     HGC_LAUNCH_CHECK();
-    grid_setup_kernel<<<1, 32, 0, stream>>>(partial, blocks, n_dims, row_splits, n_rs, n_bins_arg,
+    grid_setup_kernel<<<1, 32, 0, stream>>>(partial, blocks, n_dims, n_all, row_splits, n_rs, n_bins_arg,
                                            n_neigh, pre_normalized, grid);
     HGC_LAUNCH_CHECK();
     return HGC_OK;
@@ -169,12 +221,14 @@ int range_partial_blocks(int n_vert)
 int launch_bin_keys(const float *coords, int coord_stride, int n_dims, const float *shift,
                     const int *row_splits, int n_rs, const float *bin_width, const int *n_bins,
                     int *assigned, int *flat_out, int *sort_keys, int n_vert, int n_total_bins,
-                    const int *n_total_bins_dev, unsigned *status, cudaStream_t stream)
+                    const int *n_total_bins_dev, unsigned *status, cudaStream_t stream,
+                    const GridParams *grid, int n_all, int *sub_keys)
 {
     if (n_vert <= 0) return HGC_OK;
+    if (n_all > kMaxBinDims) n_all = kMaxBinDims;
     bin_keys_kernel<<<div_up(n_vert, 256), 256, 0, stream>>>(
             coords, coord_stride, n_dims, shift, row_splits, n_rs, bin_width, n_bins, assigned, flat_out,
-            sort_keys, n_vert, n_total_bins, n_total_bins_dev, status);
+            sort_keys, n_vert, n_total_bins, n_total_bins_dev, status, grid, n_all, grid ? sub_keys : nullptr);
     HGC_LAUNCH_CHECK();
     return HGC_OK;
 }

@@ -49,8 +49,8 @@ namespace {
 struct RaggedBuffers {
     GridParams *grid;
     float *partial;
-    int *keys, *skeys, *perm, *tkeys, *tvals, *hist, *assigned, *sassigned, *bounds, *sdir;
-    float4 *pts;
+    int *keys, *subkeys, *skeys, *perm, *k1, *v1, *tkeys, *tvals, *hist, *assigned, *sassigned, *bounds, *sdir;
+    KnnScratch knn;
 };
 
 // One definition of the layout serves both the size query (Sizer) and the real carve (Carver).
@@ -62,6 +62,9 @@ void layout(W &ws, int n_vert, int n_coords, const RaggedPlan &p, bool use_dir, 
     t.grid = ws.template take<GridParams>(1);
     t.partial = ws.template take<float>((size_t)range_partial_blocks(n_vert) * 2 * kMaxBinDims);
     t.keys = ws.template take<int>(n);
+    t.subkeys = ws.template take<int>(n);
+    t.k1 = ws.template take<int>(n);
+    t.v1 = ws.template take<int>(n);
     t.skeys = ws.template take<int>(n);
     t.perm = ws.template take<int>(n);
     t.tkeys = ws.template take<int>(n);
@@ -70,7 +73,7 @@ void layout(W &ws, int n_vert, int n_coords, const RaggedPlan &p, bool use_dir, 
     t.assigned = ws.template take<int>(n * (p.cb + 1));
     t.sassigned = ws.template take<int>(n * (p.cb + 1));
     t.bounds = ws.template take<int>((size_t)p.max_bins + 1);
-    t.pts = ws.template take<float4>(n * knn_nv4(n_coords));
+    t.knn = knn_scratch_layout(ws, n_vert, n_coords);
     t.sdir = ws.template take<int>(use_dir ? n : 0);
     if (b) *b = t;
 }
@@ -118,18 +121,27 @@ extern "C" int hgc_binned_select_knn_ragged(
     layout(ws, n_vert, n_coords, p, use_direction != 0, &b);
     HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
 
-    if (int rc = compute_grid(d_coords, n_coords, p.cb, n_vert, d_row_splits, n_rs, n_bins, n_neigh,
+    if (int rc = compute_grid(d_coords, n_coords, p.cb, n_coords, n_vert, d_row_splits, n_rs, n_bins, n_neigh,
                               /*pre_normalized=*/0, b.partial, b.grid, stream))
         return rc;
     if (int rc = launch_bin_keys(d_coords, n_coords, p.cb, b.grid->shift, d_row_splits, n_rs,
                                  &b.grid->bin_width, b.grid->n_bins, b.assigned, nullptr, b.keys, n_vert,
-                                 0, &b.grid->n_total_bins, ws.status(), stream))
+                                 0, &b.grid->n_total_bins, ws.status(), stream, b.grid, n_coords, b.subkeys))
         return rc;
-    if (int rc = sort_pairs(b.keys, nullptr, b.skeys, b.perm, b.tkeys, b.tvals, b.hist, n_vert,
+    // Order: by bin (what the reference's argsort gives), and inside a bin by the locality code
+    // instead of by original index -- a free choice, since results do not depend on it.  Two stable
+    // counting sorts, least significant key first.
+    if (int rc = sort_pairs(b.subkeys, nullptr, b.k1, b.v1, b.tkeys, b.tvals, b.hist, n_vert, kSubBits, stream))
+        return rc;
+    {
+        gather_rows_kernel<<<div_up(n_vert, 256), 256, 0, stream>>>(b.keys, 1, b.v1, b.k1, n_vert);
+        HGC_LAUNCH_CHECK();
+    }
+    if (int rc = sort_pairs(b.k1, b.v1, b.skeys, b.perm, b.tkeys, b.tvals, b.hist, n_vert,
                             bits_for(p.max_bins), stream))
         return rc;
     if (int rc = boundaries_from_sorted_keys(b.skeys, n_vert, b.bounds, (int)p.max_bins, stream)) return rc;
-    if (int rc = pack_points(d_coords, n_coords, b.perm, b.pts, n_vert, stream)) return rc;
+    if (int rc = pack_points(d_coords, n_coords, b.perm, b.knn, n_vert, stream)) return rc;
     {
         const long long total = (long long)n_vert * (p.cb + 1);
         gather_rows_kernel<<<div_up(total, 256), 256, 0, stream>>>(b.assigned, p.cb + 1, b.perm, b.sassigned, n_vert);
@@ -139,7 +151,7 @@ extern "C" int hgc_binned_select_knn_ragged(
             HGC_LAUNCH_CHECK();
         }
     }
-    if (int rc = launch_select_knn(b.pts, n_coords, b.skeys, b.sassigned, b.bounds, b.grid->n_bins,
+    if (int rc = launch_select_knn(b.knn, n_coords, b.skeys, b.sassigned, b.bounds, b.grid->n_bins,
                                    &b.grid->bin_width, use_direction ? b.sdir : nullptr, d_indices, d_dist,
                                    b.perm, b.perm, n_vert, n_neigh, p.cb, (int)p.max_bins + 1, tf_compat,
                                    use_direction != 0, ws.status(), stream))

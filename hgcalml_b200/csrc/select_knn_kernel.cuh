@@ -1,0 +1,471 @@
+// BinnedSelectKnn search kernel (device code; instantiated per coordinate width in select_knn_nv*.cu).
+//
+// One warp owns one query.  Work is organised around the reference's candidate set and stop rule
+// (modules/compiled/binned_select_knn_kernel.cc:110-192): shells of grid bins at Chebyshev distance
+// d = 0,1,2,.. around the query's bin are scanned completely; the search ends after a shell with no
+// bin inside the grid, or once the row is full and ((bw*d)*bw)*d exceeds the K-th best squared
+// distance.  Within that frame the kernel avoids work that cannot change the result:
+//
+//  * Bins that are adjacent along the last binned dimension are contiguous in bin-sorted order, so
+//    a shell becomes a handful of index ranges.
+//  * Every 32 consecutive bin-sorted hits form a chunk with a bounding box over all coordinates
+//    (chunk_aabb_kernel).  Long ranges are scanned chunk by chunk, nearest box first, and a chunk
+//    is skipped when the box's distance to the query already exceeds the current K-th best: with
+//    the same unfused subtract/multiply/add sequence as the point distance, rounding is monotone,
+//    so no point of the chunk can have a smaller computed distance than the box.
+//  * Short ranges (sparse regions) are laid end to end and walked 32 candidates at a time.
+//
+// The best K-1 candidates live in registers as a sorted list striped over the lanes (rank r in
+// register r/32 of lane r%32), keyed by (distance bits, index) in one 64-bit word so that ties
+// fall to the lower index.  Candidates that beat the current K-th best are parked in a per-warp
+// shared-memory buffer of 32; a full buffer is sorted with a warp-shuffle bitonic network and
+// merged into the list.  Distances are computed with separately rounded operations in coordinate
+// order, so they are bit-identical to the CPU op (binned_select_knn_kernel.cc:19-29).
+#pragma once
+#include "common.cuh"
+#include "select_knn.cuh"
+
+namespace hgc {
+
+// A candidate is one 64-bit word: squared-distance bits in the high half, hit index in the low
+// half, so that ordering the words orders by (distance, index).  The word is held as a double:
+// for non-negative floats in the high half the IEEE-754 order of the doubles equals the order of
+// the 64-bit integers (distances are never NaN), and a 64-bit comparison then is one FP64
+// instruction instead of a chain of integer compares on the (half-rate, saturated) integer pipe.
+typedef double knn_key;
+#define HGC_KNN_INF_KEY 1.7976931348623157e308  /* DBL_MAX: above every real key, even distance = +inf */
+#ifdef HGC_KNN_STATS
+#define HGC_STAT(x) x
+#else
+#define HGC_STAT(x)
+#endif
+constexpr int kKnnWarps = 8;
+constexpr int kKnnThreads = kKnnWarps * kWarp;
+constexpr int kQueriesPerBlock = 64;   // consecutive bin-sorted queries handled by one block
+
+__device__ __forceinline__ knn_key make_key(float distsq, int j)
+{
+    return __hiloint2double((int)__float_as_uint(distsq), j);
+}
+__device__ __forceinline__ float key_distsq(knn_key k) { return __int_as_float(__double2hiint(k)); }
+__device__ __forceinline__ int key_index(knn_key k) { return __double2loint(k); }
+
+__device__ __forceinline__ knn_key shfl_key(knn_key v, int src) { return __shfl_sync(0xffffffffu, v, src); }
+__device__ __forceinline__ knn_key shfl_xor_key(knn_key v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+
+// Keeps the smaller of (v, o) when `lower`, else the larger.
+__device__ __forceinline__ knn_key cmp_exchange(knn_key v, knn_key o, bool lower)
+{
+    return ((v < o) == lower) ? v : o;
+}
+
+// Ascending bitonic sort of one key per lane.  Each merge starts with the mirrored partner, so
+// every step is "the lower lane keeps the smaller key" and only five lane-bit tests are needed.
+__device__ __forceinline__ knn_key warp_sort(knn_key v, int lane)
+{
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+        v = cmp_exchange(v, shfl_xor_key(v, k - 1), (lane & (k >> 1)) == 0);
+#pragma unroll
+        for (int j = k >> 2; j > 0; j >>= 1) v = cmp_exchange(v, shfl_xor_key(v, j), (lane & j) == 0);
+    }
+    return v;
+}
+
+// Sorts a bitonic sequence (one key per lane) ascending.
+__device__ __forceinline__ knn_key warp_bitonic_merge(knn_key v, int lane)
+{
+#pragma unroll
+    for (int j = 16; j > 0; j >>= 1) v = cmp_exchange(v, shfl_xor_key(v, j), (lane & j) == 0);
+    return v;
+}
+
+// Merges an ascending block `b` of 32 keys into the ascending striped list, keeping the smallest.
+template <int L>
+__device__ __forceinline__ void merge_into_list(knn_key (&list)[L], knn_key b, int lane)
+{
+#pragma unroll
+    for (int r = 0; r < L; r++) {
+        // a register whose largest key is not above b's smallest stays as it is
+        const knn_key reg_max = shfl_key(list[r], 31);
+        const knn_key b_min = shfl_key(b, 0);
+        if (b_min >= reg_max) continue;
+        const knn_key rev = shfl_xor_key(b, 31);
+        const bool keep = list[r] < rev;
+        const knn_key lo = keep ? list[r] : rev;
+        const knn_key hi = keep ? rev : list[r];
+        list[r] = warp_bitonic_merge(lo, lane);
+        if (r + 1 < L) b = warp_bitonic_merge(hi, lane);
+    }
+}
+
+// list[reg] for a runtime `reg`, without indexing the register array dynamically
+template <int L>
+__device__ __forceinline__ knn_key list_reg(const knn_key (&list)[L], int reg)
+{
+    knn_key v = list[0];
+#pragma unroll
+    for (int r = 1; r < L; r++)
+        if (r == reg) v = list[r];
+    return v;
+}
+
+template <int NV4>
+struct Point {
+    float4 v[NV4];
+};
+
+template <int NV4>
+__device__ __forceinline__ Point<NV4> load_point(const float4 *__restrict__ pts, size_t i)
+{
+    Point<NV4> p;
+#pragma unroll
+    for (int u = 0; u < NV4; u++) p.v[u] = __ldg(pts + i * NV4 + u);
+    return p;
+}
+
+// sum over coordinates of (a-b)^2, each operation rounded on its own, in coordinate order.  The
+// zero padding of the last float4 adds +0 terms, which change nothing.
+template <int NV4>
+__device__ __forceinline__ float distsq(const Point<NV4> &a, const Point<NV4> &b)
+{
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV4; u++) {
+        float t;
+        t = __fsub_rn(a.v[u].x, b.v[u].x); s = __fadd_rn(s, __fmul_rn(t, t));
+        t = __fsub_rn(a.v[u].y, b.v[u].y); s = __fadd_rn(s, __fmul_rn(t, t));
+        t = __fsub_rn(a.v[u].z, b.v[u].z); s = __fadd_rn(s, __fmul_rn(t, t));
+        t = __fsub_rn(a.v[u].w, b.v[u].w); s = __fadd_rn(s, __fmul_rn(t, t));
+    }
+    return s;
+}
+
+// Squared distance from q to the box [lo, hi], with the operation sequence of distsq: a lower
+// bound of the computed distance to any point inside the box.
+__device__ __forceinline__ float gap1(float q, float lo, float hi)
+{
+    return fmaxf(fmaxf(__fsub_rn(lo, q), __fsub_rn(q, hi)), 0.f);
+}
+template <int NV4>
+__device__ __forceinline__ float box_distsq(const Point<NV4> &q, const float4 *__restrict__ lo,
+                                            const float4 *__restrict__ hi, size_t chunk)
+{
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV4; u++) {
+        const float4 l = __ldg(lo + chunk * NV4 + u), h = __ldg(hi + chunk * NV4 + u);
+        float g;
+        g = gap1(q.v[u].x, l.x, h.x); s = __fadd_rn(s, __fmul_rn(g, g));
+        g = gap1(q.v[u].y, l.y, h.y); s = __fadd_rn(s, __fmul_rn(g, g));
+        g = gap1(q.v[u].z, l.z, h.z); s = __fadd_rn(s, __fmul_rn(g, g));
+        g = gap1(q.v[u].w, l.w, h.w); s = __fadd_rn(s, __fmul_rn(g, g));
+    }
+    return s;
+}
+
+template <int NV4, int L, bool USE_DIR>
+struct Query {
+    knn_key list[L];
+    knn_key thr;        // key of the current K-th best; everything passes until the row is full
+    int buffered;
+    int thr_reg, thr_lane, lane, self;
+    Point<NV4> q;
+    knn_key *buf;   // this warp's shared buffer of 64 parked keys
+#ifdef HGC_KNN_STATS
+    unsigned n_offered, n_accepted, n_flushes, n_steps;  // work counters (tuning aid)
+#endif
+    const float4 *pts;
+    const int *direction;
+
+    __device__ __forceinline__ float kth() const
+    {
+        return thr == HGC_KNN_INF_KEY ? INFINITY : key_distsq(thr);
+    }
+    // Folds the first 32 parked keys into the list; later ones move to the front of the buffer.
+    __device__ __forceinline__ void flush()
+    {
+        __syncwarp();
+        knn_key b = lane < buffered ? buf[lane] : HGC_KNN_INF_KEY;
+        const knn_key rest = (lane + kWarp < buffered) ? buf[lane + kWarp] : HGC_KNN_INF_KEY;
+        __syncwarp();
+        if (lane + kWarp < buffered) buf[lane] = rest;
+        buffered = buffered > kWarp ? buffered - kWarp : 0;
+        b = warp_sort(b, lane);
+        merge_into_list<L>(list, b, lane);
+        thr = shfl_key(list_reg<L>(list, thr_reg), thr_lane);
+        HGC_STAT(n_flushes++);
+        __syncwarp();
+    }
+    // One candidate per lane (or none).  Uniform control flow: call with all 32 lanes.
+    __device__ __forceinline__ void offer(bool valid, int j)
+    {
+        bool pass = false;
+        knn_key key = HGC_KNN_INF_KEY;
+        if (valid) {
+            const Point<NV4> p = load_point<NV4>(pts, (size_t)j);
+            const float ds = distsq<NV4>(q, p);
+            key = make_key(ds, j);
+            pass = j != self && key < thr;
+            if (USE_DIR && pass) {
+                const int dj = direction[j];
+                pass = !(dj == 1 || dj == 2);
+            }
+        }
+        HGC_STAT(n_steps++);
+        HGC_STAT(n_offered += __popc(__ballot_sync(0xffffffffu, valid)));
+        const unsigned m = __ballot_sync(0xffffffffu, pass);
+        if (m == 0u) return;
+        // fewer than 32 keys are parked on entry, so these at most 32 more always fit into the 64 slots
+        if (pass) buf[buffered + __popc(m & ((1u << lane) - 1u))] = key;
+        buffered += __popc(m);
+        HGC_STAT(n_accepted += __popc(m));
+        if (buffered >= kWarp) flush();
+    }
+};
+
+template <int NV4, int L, int CB, bool USE_DIR>
+__global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a)
+{
+    __shared__ knn_key s_buf[kKnnWarps][2 * kWarp];
+    __shared__ int s_start[kKnnWarps][kWarp];
+    __shared__ int s_end[kKnnWarps][kWarp];  // inclusive prefix of the short ranges' lengths
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = a.K;
+    const int want = K - 1;  // neighbours besides the query itself
+    const float bw = a.bin_width[0];
+
+    int nb[CB], stride[CB];
+    {
+        int s = 1;
+#pragma unroll
+        for (int d = CB - 1; d >= 0; d--) { nb[d] = a.n_bins[d]; stride[d] = s; s *= nb[d]; }
+    }
+    const int bins_per_event = stride[0] * nb[0];
+
+    const int q_begin = blockIdx.x * kQueriesPerBlock;
+    const int q_end = min(q_begin + kQueriesPerBlock, a.n_vert);
+
+    for (int i = q_begin + warp; i < q_end; i += kKnnWarps) {
+        const int out_row = a.row_map ? a.row_map[i] : i;
+        const int self_id = a.id_map ? a.id_map[i] : i;
+        int *row_idx = a.out_idx + (size_t)out_row * K;
+        float *row_dist = a.out_dist + (size_t)out_row * K;
+
+        Query<NV4, L, USE_DIR> Q;
+#pragma unroll
+        for (int r = 0; r < L; r++) Q.list[r] = HGC_KNN_INF_KEY;
+        Q.thr = HGC_KNN_INF_KEY;
+        Q.buffered = 0;
+        HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0);
+        HGC_STAT(unsigned n_boxes = 0; unsigned n_chunks = 0);
+        Q.lane = lane;
+        Q.self = i;
+        Q.buf = s_buf[warp];
+        Q.pts = reinterpret_cast<const float4 *>(a.pts);
+        Q.direction = a.direction;
+        Q.thr_reg = want > 0 ? (want - 1) / 32 : 0;
+        Q.thr_lane = want > 0 ? (want - 1) % 32 : 0;
+
+        bool searching = true;
+        if (USE_DIR) {
+            const int dir = a.direction[i];
+            if (dir == 0 || dir == 2) searching = false;  // may not have neighbours: defaults only
+        }
+
+        if (searching && want > 0) {
+            Q.q = load_point<NV4>(Q.pts, (size_t)i);
+            int qb[CB];
+#pragma unroll
+            for (int d = 0; d < CB; d++) qb[d] = a.dim_bin_idx[(size_t)i * (CB + 1) + 1 + d];
+            const int event_offset = bins_per_event * (a.bin_idx[i] / bins_per_event);
+
+            // Shells 0 and 1 are always both scanned (the stop rule cannot fire at d = 0), so the
+            // first pass covers the whole 3^CB cube; later passes cover one shell each.
+            for (int d = 1;; d++) {
+                // in-grid extent of the shell's bounding cube in the leading CB-1 dimensions
+                int lo[CB], span[CB], cells = 1, centre = 0;
+#pragma unroll
+                for (int k = 0; k < CB - 1; k++) {
+                    lo[k] = max(qb[k] - d, 0);
+                    span[k] = min(qb[k] + d, nb[k] - 1) - lo[k] + 1;
+                    centre = centre * span[k] + (qb[k] - lo[k]);
+                    cells *= span[k];
+                }
+                const int last_lo = qb[CB - 1] - d, last_hi = qb[CB - 1] + d;
+                const int last_lo_c = max(last_lo, 0), last_hi_c = min(last_hi, nb[CB - 1] - 1);
+                bool shell_in_grid = false;
+
+                // two range slots per cell: a full row (surface cells, or every cell in the first
+                // pass) or the two end bins of the row.  Cells are visited starting at the query's
+                // own row, which tightens the K-th best early.
+                for (int base = 0; base < 2 * cells; base += kWarp) {
+                    const int slot = base + lane;
+                    int start = 0, len = 0;
+                    bool slot_in_grid = false;
+                    if (slot < 2 * cells) {
+                        int c = (slot >> 1) + centre, flat = 0;
+                        if (c >= cells) c -= cells;
+                        bool surface = d == 1;
+#pragma unroll
+                        for (int k = CB - 2; k >= 0; k--) {
+                            const int g = lo[k] + c % span[k];
+                            c /= span[k];
+                            flat += g * stride[k];
+                            const int off = g - qb[k];
+                            surface = surface || off == d || off == -d;
+                        }
+                        int b0 = -1, b1 = -1;
+                        if (surface) {
+                            if ((slot & 1) == 0) { b0 = last_lo_c; b1 = last_hi_c; }
+                        } else if ((slot & 1) == 0) {
+                            if (last_lo >= 0) b0 = b1 = last_lo;
+                        } else {
+                            if (last_hi < nb[CB - 1]) b0 = b1 = last_hi;
+                        }
+                        if (b0 >= 0 && b0 <= b1) {
+                            const int g0 = event_offset + flat + b0, g1 = event_offset + flat + b1;
+                            if (g1 < a.n_bboundaries - 1) {
+                                slot_in_grid = true;
+                                start = a.bin_boundaries[g0];
+                                len = a.bin_boundaries[g1 + 1] - start;
+                            } else {
+                                flag_status(a.status, HGC_STATUS_FLAT_BIN_OVERFLOW);
+                            }
+                        }
+                    }
+                    shell_in_grid = shell_in_grid || __any_sync(0xffffffffu, slot_in_grid);
+
+                    // ---- long ranges: chunk by chunk, nearest bounding box first ----
+                    unsigned long_mask = __ballot_sync(0xffffffffu, len > a.long_range);
+                    while (long_mask) {
+                        const int src = __ffs(long_mask) - 1;
+                        long_mask &= long_mask - 1;
+                        const int r_begin = __shfl_sync(0xffffffffu, start, src);
+                        const int r_end = r_begin + __shfl_sync(0xffffffffu, len, src);
+                        const int c_last = (r_end - 1) >> 5;
+                        for (int cb0 = r_begin >> 5; cb0 <= c_last; cb0 += kWarp) {
+                            const int chunk = cb0 + lane;
+                            float lb = INFINITY;
+                            if (chunk <= c_last) lb = box_distsq<NV4>(Q.q, a.chunk_lo, a.chunk_hi, (size_t)chunk);
+                            unsigned alive = __ballot_sync(0xffffffffu, chunk <= c_last && lb <= Q.kth());
+                            HGC_STAT(n_boxes += min(c_last - cb0 + 1, kWarp));
+                            while (alive) {
+                                const int cl = __ffs(alive) - 1;
+                                alive &= alive - 1;
+                                // the K-th best may have tightened since the box test
+                                if (__shfl_sync(0xffffffffu, lb, cl) > Q.kth()) continue;
+                                HGC_STAT(n_chunks++);
+                                const int j = ((cb0 + cl) << 5) + lane;
+                                Q.offer(j >= r_begin && j < r_end, j);
+                            }
+                        }
+                    }
+
+                    // ---- short ranges: laid end to end, 32 candidates per step ----
+                    const int slen = len > a.long_range ? 0 : len;
+                    int incl = slen;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    const int total = __shfl_sync(0xffffffffu, incl, 31);
+                    if (total == 0) continue;
+                    __syncwarp();
+                    s_start[warp][lane] = start - (incl - slen);  // so that j = s_start[r] + v
+                    s_end[warp][lane] = incl;
+                    __syncwarp();
+                    int r = 0;
+                    for (int t0 = 0; t0 < total; t0 += kWarp) {
+                        const int v = t0 + lane;
+                        int j = 0;
+                        if (v < total) {
+                            while (v >= s_end[warp][r]) r++;
+                            j = s_start[warp][r] + v;
+                        }
+                        Q.offer(v < total, j);
+                    }
+                }
+
+                // end of shell: fold the parked candidates in, then apply the stop rule
+                while (Q.buffered > 0) Q.flush();
+                if (!shell_in_grid) break;
+                if (Q.thr != HGC_KNN_INF_KEY) {
+                    const float df = (float)d;
+                    const float reach = __fmul_rn(__fmul_rn(__fmul_rn(bw, df), bw), df);
+                    if (reach > Q.kth()) break;
+                }
+                if (d > (1 << 20)) { flag_status(a.status, HGC_STATUS_ITERATION_CAP); break; }
+            }
+        }
+
+#ifdef HGC_KNN_STATS
+        if (a.stats && lane == 0) {
+            atomicAdd(&a.stats[0], 1ull);
+            atomicAdd(&a.stats[1], (unsigned long long)Q.n_offered);
+            atomicAdd(&a.stats[2], (unsigned long long)Q.n_accepted);
+            atomicAdd(&a.stats[3], (unsigned long long)Q.n_flushes);
+            atomicAdd(&a.stats[4], (unsigned long long)n_boxes);
+            atomicAdd(&a.stats[5], (unsigned long long)n_chunks);
+            atomicAdd(&a.stats[6], (unsigned long long)Q.n_steps);
+        }
+#endif
+        // write the row: slot 0 = the query, slots 1.. = list ranks 0.. (ascending)
+        const int pad = a.tf_compat ? self_id : -1;
+        if (lane == 0) { row_idx[0] = self_id; row_dist[0] = 0.f; }
+#pragma unroll
+        for (int r = 0; r < L; r++) {
+            const int slot = 1 + r * 32 + lane;
+            if (slot < K) {
+                const knn_key key = Q.list[r];
+                int id = pad;
+                float ds = 0.f;
+                if (key != HGC_KNN_INF_KEY) {
+                    const int j = key_index(key);
+                    id = a.id_map ? a.id_map[j] : j;
+                    ds = key_distsq(key);
+                }
+                row_idx[slot] = id;
+                row_dist[slot] = ds;
+            }
+        }
+    }
+}
+
+template <int NV4, int L, int CB>
+int launch_knn3(const KnnArgs &a, bool use_dir, cudaStream_t stream)
+{
+    const int blocks = div_up(a.n_vert, kQueriesPerBlock);
+    if (use_dir) select_knn_kernel<NV4, L, CB, true><<<blocks, kKnnThreads, 0, stream>>>(a);
+    else         select_knn_kernel<NV4, L, CB, false><<<blocks, kKnnThreads, 0, stream>>>(a);
+    HGC_LAUNCH_CHECK();
+    return HGC_OK;
+}
+
+template <int NV4, int L>
+int launch_knn2(const KnnArgs &a, int cb, bool use_dir, cudaStream_t stream)
+{
+    switch (cb) {
+        case 2: return launch_knn3<NV4, L, 2>(a, use_dir, stream);
+        case 3: return launch_knn3<NV4, L, 3>(a, use_dir, stream);
+        case 4: return launch_knn3<NV4, L, 4>(a, use_dir, stream);
+        case 5: return launch_knn3<NV4, L, 5>(a, use_dir, stream);
+    }
+    return HGC_ERR_UNSUPPORTED;
+}
+
+template <int NV4>
+int launch_knn_nv(const KnnArgs &a, int cb, bool use_dir, cudaStream_t stream)
+{
+    const int want = a.K - 1;
+    if (want <= 32) return launch_knn2<NV4, 1>(a, cb, use_dir, stream);
+    if (want <= 64) return launch_knn2<NV4, 2>(a, cb, use_dir, stream);
+    if (want <= 128) return launch_knn2<NV4, 4>(a, cb, use_dir, stream);
+    if (want <= 256) return launch_knn2<NV4, 8>(a, cb, use_dir, stream);
+    if (want <= 512) return launch_knn2<NV4, 16>(a, cb, use_dir, stream);
+    return HGC_ERR_UNSUPPORTED;
+}
+
+}  // namespace hgc

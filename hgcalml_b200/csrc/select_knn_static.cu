@@ -10,9 +10,11 @@ namespace {
 constexpr int kStaticMaxVert = HGC_STATIC_KNN_MAX_VERT;
 constexpr int kStaticMaxCoords = HGC_STATIC_KNN_MAX_COORDS;
 constexpr int kMaxDevices = 64;
-constexpr size_t kStaticBytes = hgc::kAlign + (size_t)kStaticMaxVert * sizeof(float4);
+// status word + packed points + two bounding-box arrays (one box per 32 hits), each 256-byte aligned
+constexpr size_t kStaticBytes = hgc::kAlign + (size_t)kStaticMaxVert * sizeof(float4) +
+                                2 * ((size_t)kStaticMaxVert / 32) * sizeof(float4);
 
-// Every GPU that loads the library carries this array until the process exits (4 MiB + 256 B).
+// Every GPU that loads the library carries this array until the process exits (4.25 MiB + 256 B).
 // All calls on a device share it and it keeps the previous call's contents.
 static __device__ __align__(256) unsigned char g_knn_scratch[kStaticBytes];
 
@@ -61,11 +63,11 @@ extern "C" int hgc_binned_select_knn_static(
     void *scratch = nullptr;
     if (int rc = scratch_for_current_device(&scratch)) return rc;
     Carver ws(scratch);
-    // the status word must start at zero; the packed points are rewritten for all n_vert hits
+    // the status word must start at zero; packed points and boxes are rewritten for all n_vert hits
     HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
-    float4 *pts = ws.take<float4>((size_t)n_vert * knn_nv4(n_coords));
-    if (int rc = pack_points(d_coord, n_coords, nullptr, pts, n_vert, stream)) return rc;
-    return launch_select_knn(pts, n_coords, d_bin_idx, d_dim_bin_idx, d_bin_boundaries, d_n_bins,
+    const KnnScratch s = knn_scratch_layout(ws, n_vert, n_coords);
+    if (int rc = pack_points(d_coord, n_coords, nullptr, s, n_vert, stream)) return rc;
+    return launch_select_knn(s, n_coords, d_bin_idx, d_dim_bin_idx, d_bin_boundaries, d_n_bins,
                              d_bin_width, d_direction, d_indices, d_dist, nullptr, nullptr, n_vert,
                              n_neigh, n_bin_dim, n_bboundaries, tf_compat, use_direction != 0,
                              ws.status(), stream);

@@ -102,7 +102,7 @@ int hgc_binned_select_knn(
  * fails or is forbidden by the deployment's rules.  For them this entry takes the same arguments
  * as hgc_binned_select_knn minus the workspace and computes the same result, keeping its scratch
  * (a status word and the packed coordinates) in a fixed array that is part of the library's device
- * image: 4 MiB + 256 bytes on every GPU that loads the library, held until the process exits.
+ * image: 4.25 MiB + 256 bytes on every GPU that loads the library, held until the process exits.
  * It calls no cudaMalloc / cudaFree and no allocating library routine.
  *
  * Limits: n_vert <= HGC_STATIC_KNN_MAX_VERT and n_coords <= HGC_STATIC_KNN_MAX_COORDS, otherwise
