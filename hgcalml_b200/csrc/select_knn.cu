@@ -8,7 +8,7 @@ namespace hgc {
 namespace {
 
 // work counters of the search kernel, filled only while HGC_KNN_STATS is set in the environment
-__device__ unsigned long long g_knn_stats[8];
+__device__ unsigned long long g_knn_stats[16];
 
 // [n_vert, n_coords] floats (optionally gathered through perm) -> zero-padded float4 records
 __global__ void pack_points_kernel(const float *__restrict__ coords, int n_coords, int nv4,
@@ -106,12 +106,13 @@ int launch_select_knn(const KnnScratch &s, int n_coords, const int *bin_idx, con
 using namespace hgc;
 
 // Tuning aid: copies the search kernel's work counters (queries, candidates offered, accepted,
-// list merges, boxes tested, chunks scanned, steps, unused) to the host and clears them.
-extern "C" int hgc_debug_knn_stats(unsigned long long *out8)
+// list merges, boxes tested, chunks scanned, steps, then cycles: per query, in merges, in candidate
+// steps; filled only by a build with -DHGC_KNN_STATS) to the host and clears them.
+extern "C" int hgc_debug_knn_stats(unsigned long long *out16)
 {
     HGC_CUDA_TRY(cudaDeviceSynchronize());
-    HGC_CUDA_TRY(cudaMemcpyFromSymbol(out8, g_knn_stats, sizeof(unsigned long long) * 8));
-    unsigned long long zero[8] = {0};
+    HGC_CUDA_TRY(cudaMemcpyFromSymbol(out16, g_knn_stats, sizeof(unsigned long long) * 16));
+    unsigned long long zero[16] = {0};
     HGC_CUDA_TRY(cudaMemcpyToSymbol(g_knn_stats, zero, sizeof(zero)));
     return HGC_OK;
 }

@@ -174,6 +174,7 @@ struct Query {
     knn_key *buf;   // this warp's shared buffer of 64 parked keys
 #ifdef HGC_KNN_STATS
     unsigned n_offered, n_accepted, n_flushes, n_steps;  // work counters (tuning aid)
+    long long t_flush, t_offer;
 #endif
     const float4 *pts;
     const int *direction;
@@ -182,23 +183,33 @@ struct Query {
     {
         return thr == HGC_KNN_INF_KEY ? INFINITY : key_distsq(thr);
     }
-    // Folds the first 32 parked keys into the list; later ones move to the front of the buffer.
+    // Folds the first 32 parked keys into the list; later ones that still beat the new K-th best
+    // move to the front of the buffer.
     __device__ __forceinline__ void flush()
     {
+        HGC_STAT(const long long t0 = clock64());
         __syncwarp();
         knn_key b = lane < buffered ? buf[lane] : HGC_KNN_INF_KEY;
         const knn_key rest = (lane + kWarp < buffered) ? buf[lane + kWarp] : HGC_KNN_INF_KEY;
-        __syncwarp();
-        if (lane + kWarp < buffered) buf[lane] = rest;
-        buffered = buffered > kWarp ? buffered - kWarp : 0;
         b = warp_sort(b, lane);
         merge_into_list<L>(list, b, lane);
         thr = shfl_key(list_reg<L>(list, thr_reg), thr_lane);
+        const bool keep = rest < thr;
+        const unsigned m = __ballot_sync(0xffffffffu, keep);
+        if (keep) buf[__popc(m & ((1u << lane) - 1u))] = rest;
+        buffered = __popc(m);
         HGC_STAT(n_flushes++);
         __syncwarp();
+        HGC_STAT(t_flush += clock64() - t0);
     }
     // One candidate per lane (or none).  Uniform control flow: call with all 32 lanes.
     __device__ __forceinline__ void offer(bool valid, int j)
+    {
+        HGC_STAT(const long long t0 = clock64(); const long long f0 = t_flush);
+        offer_inner(valid, j);
+        HGC_STAT(t_offer += (clock64() - t0) - (t_flush - f0));
+    }
+    __device__ __forceinline__ void offer_inner(bool valid, int j)
     {
         bool pass = false;
         knn_key key = HGC_KNN_INF_KEY;
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
         for (int r = 0; r < L; r++) Q.list[r] = HGC_KNN_INF_KEY;
         Q.thr = HGC_KNN_INF_KEY;
         Q.buffered = 0;
-        HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0);
+        HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0; Q.t_flush = Q.t_offer = 0; const long long t_query0 = clock64());
         HGC_STAT(unsigned n_boxes = 0; unsigned n_chunks = 0);
         Q.lane = lane;
         Q.self = i;
@@ -286,10 +297,12 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
             for (int d = 1;; d++) {
                 // in-grid extent of the shell's bounding cube in the leading CB-1 dimensions
                 int lo[CB], span[CB], cells = 1, centre = 0;
+                float inv_span[CB];
 #pragma unroll
                 for (int k = 0; k < CB - 1; k++) {
                     lo[k] = max(qb[k] - d, 0);
                     span[k] = min(qb[k] + d, nb[k] - 1) - lo[k] + 1;
+                    inv_span[k] = __frcp_rn((float)span[k]);
                     centre = centre * span[k] + (qb[k] - lo[k]);
                     cells *= span[k];
                 }
@@ -310,8 +323,15 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                         bool surface = d == 1;
 #pragma unroll
                         for (int k = CB - 2; k >= 0; k--) {
-                            const int g = lo[k] + c % span[k];
-                            c /= span[k];
+                            int quot;
+                            if (cells <= 4096) {
+                                // exact for these sizes: (c + 0.5) / span is at least 0.5/61 away from an integer
+                                quot = (int)(((float)c + 0.5f) * inv_span[k]);
+                            } else {
+                                quot = c / span[k];
+                            }
+                            const int g = lo[k] + (c - quot * span[k]);
+                            c = quot;
                             flat += g * stride[k];
                             const int off = g - qb[k];
                             surface = surface || off == d || off == -d;
@@ -410,6 +430,9 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
             atomicAdd(&a.stats[4], (unsigned long long)n_boxes);
             atomicAdd(&a.stats[5], (unsigned long long)n_chunks);
             atomicAdd(&a.stats[6], (unsigned long long)Q.n_steps);
+            atomicAdd(&a.stats[7], (unsigned long long)(clock64() - t_query0));
+            atomicAdd(&a.stats[8], (unsigned long long)Q.t_flush);
+            atomicAdd(&a.stats[9], (unsigned long long)Q.t_offer);
         }
 #endif
         // write the row: slot 0 = the query, slots 1.. = list ranks 0.. (ascending)
