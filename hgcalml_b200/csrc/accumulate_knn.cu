@@ -8,31 +8,58 @@
 // multiply and add, which makes the mean bit-identical to the CPU op
 // (modules/compiled/accumulate_knn_kernel.cc:48-81); the max is reset by slot 0 and later slots win
 // ties, as there.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace hgc {
 namespace {
 
 constexpr int kAccThreads = 256;
+constexpr int kAccTile = 512;  // consecutive hits a block processes before it jumps to its next tile
 
-template <int LPH, int VPL, bool EXP, bool WITH_ARG>
-__global__ void __launch_bounds__(kAccThreads)
+// Packed float32x2 arithmetic (two independent, individually rounded float32 operations per
+// instruction on sm_100): same results as scalar __fmul_rn / __fadd_rn, half the issue slots.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b)
+{
+    float2 r;
+    asm("{ .reg .b64 ra, rb, rr; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mul.rn.f32x2 rr, ra, rb; "
+        "mov.b64 {%0,%1}, rr; }"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b)
+{
+    float2 r;
+    asm("{ .reg .b64 ra, rb, rr; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; add.rn.f32x2 rr, ra, rb; "
+        "mov.b64 {%0,%1}, rr; }"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+
+template <int LPH, int VPL, int CH, int MINB, bool EXP, bool WITH_ARG>
+__global__ void __launch_bounds__(kAccThreads, MINB)
 accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restrict__ feat,
                       const int *__restrict__ idxs, float *__restrict__ out, int *__restrict__ out_arg,
                       int n_vert, int K, int F4, int n_out_feat, bool mean_and_max,
                       const int *__restrict__ order, float scale)
 {
     constexpr int kGroupsPerBlock = kAccThreads / LPH;
-    constexpr int CH = LPH < 8 ? LPH : 8;  // neighbour rows requested before the arithmetic starts
-    const int gl = threadIdx.x % LPH;      // lane inside the group
+    static_assert(LPH % CH == 0 || CH > LPH, "chunking");
+    constexpr int CHN = CH < LPH ? CH : LPH;  // neighbour rows requested before the arithmetic starts
+    const int gl = threadIdx.x % LPH;         // lane inside the group
     const int group_in_block = threadIdx.x / LPH;
+    const unsigned group_mask = LPH == 32 ? 0xffffffffu : (((1u << LPH) - 1u) << ((threadIdx.x & 31) / LPH * LPH));
     const float inv_count = (float)K;
 
-    for (long long g = (long long)blockIdx.x * kGroupsPerBlock + group_in_block;;
-         g += (long long)gridDim.x * kGroupsPerBlock) {
-        // whole warps leave together: a warp's groups are consecutive g
-        const long long warp_first = g - (group_in_block % (kWarp / LPH));
-        if (warp_first >= n_vert) break;
+    // A block walks tiles of kAccTile consecutive hits (of the processing order), kGroupsPerBlock at a
+    // time: with a spatially coherent order the neighbour rows of one step are still in L1 for the next.
+    constexpr int kStepsPerTile = kAccTile / kGroupsPerBlock;
+    const long long n_tiles = ((long long)n_vert + kAccTile - 1) / kAccTile;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x)
+    for (int step = 0; step < kStepsPerTile; step++) {
+        const long long g0 = tile * kAccTile + (long long)step * kGroupsPerBlock;
+        if (g0 >= n_vert) break;  // uniform over the block
+        const long long g = g0 + group_in_block;
         const bool live = g < n_vert;
         const int v = live ? (order ? order[g] : (int)g) : 0;
 
@@ -45,49 +72,92 @@ accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restric
             arg[u] = make_int4(0, 0, 0, 0);
         }
 
+        // indices / weights of the next LPH slots are requested one chunk ahead of their use
+        int next_j = -1;
+        float next_w = 0.f;
+        if (live && gl < K) {
+            next_j = idxs[(size_t)v * K + gl];
+            next_w = weights[(size_t)v * K + gl];
+        }
         for (int c0 = 0; c0 < K; c0 += LPH) {
-            int my_j = -1;
-            float my_w = 0.f;
-            if (live && c0 + gl < K) {
-                my_j = idxs[(size_t)v * K + c0 + gl];
-                my_w = weights[(size_t)v * K + c0 + gl];
+            int my_j = next_j;
+            float my_w = next_w;
+            next_j = -1;
+            next_w = 0.f;
+            if (live && c0 + LPH + gl < K) {
+                next_j = idxs[(size_t)v * K + c0 + LPH + gl];
+                next_w = weights[(size_t)v * K + c0 + LPH + gl];
+            }
+            if (my_j >= 0) {
                 if (EXP) my_w = expf(-__fmul_rn(scale, my_w));
                 if (my_j >= n_vert) my_j = -1;
             }
+            // A chunk of LPH valid neighbours (the common case) runs without per-neighbour tests.
+            const bool dense = (__ballot_sync(0xffffffffu, my_j >= 0) & group_mask) == group_mask;
+            if (dense) {
+                if (c0 == 0) {
+                    // slot 0 is valid, so it resets the running maximum: start below everything
 #pragma unroll
-            for (int s0 = 0; s0 < LPH; s0 += CH) {
-                int j[CH];
-                float w[CH];
-                float4 f[CH][VPL];
-#pragma unroll
-                for (int kk = 0; kk < CH; kk++) {
-                    j[kk] = __shfl_sync(0xffffffffu, my_j, s0 + kk, LPH);
-                    w[kk] = __shfl_sync(0xffffffffu, my_w, s0 + kk, LPH);
-#pragma unroll
-                    for (int u = 0; u < VPL; u++) {
-                        const int vec = gl + u * LPH;
-                        f[kk][u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (j[kk] >= 0 && vec < F4) f[kk][u] = __ldg(feat + (size_t)j[kk] * F4 + vec);
-                    }
+                    for (int u = 0; u < VPL; u++) best[u] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
                 }
 #pragma unroll
-                for (int kk = 0; kk < CH; kk++) {
-                    if (j[kk] < 0) continue;
-                    const bool first = (c0 + s0 + kk) == 0;
+                for (int s0 = 0; s0 < LPH; s0 += CHN) {
+                    int j[CHN];
+                    float w[CHN];
+                    float4 f[CHN][VPL];
 #pragma unroll
-                    for (int u = 0; u < VPL; u++) {
+                    for (int kk = 0; kk < CHN; kk++) {
+                        j[kk] = __shfl_sync(0xffffffffu, my_j, s0 + kk, LPH);
+                        w[kk] = __shfl_sync(0xffffffffu, my_w, s0 + kk, LPH);
+#pragma unroll
+                        for (int u = 0; u < VPL; u++) {
+                            const int vec = gl + u * LPH;
+                            f[kk][u] = __ldg(feat + (size_t)j[kk] * F4 + (vec < F4 ? vec : 0));
+                        }
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < CHN; kk++) {
+                        const float2 w2 = make_float2(w[kk], w[kk]);
+#pragma unroll
+                        for (int u = 0; u < VPL; u++) {
+                            const float2 t01 = mul2(make_float2(f[kk][u].x, f[kk][u].y), w2);
+                            const float2 t23 = mul2(make_float2(f[kk][u].z, f[kk][u].w), w2);
+                            const float2 s01 = add2(make_float2(sum[u].x, sum[u].y), t01);
+                            const float2 s23 = add2(make_float2(sum[u].z, sum[u].w), t23);
+                            sum[u] = make_float4(s01.x, s01.y, s23.x, s23.y);
+#define HGC_MAX(comp, t)                                  \
+    if ((t) >= best[u].comp) {                            \
+        best[u].comp = (t);                               \
+        if (WITH_ARG) arg[u].comp = j[kk];                \
+    }
+                            HGC_MAX(x, t01.x) HGC_MAX(y, t01.y) HGC_MAX(z, t23.x) HGC_MAX(w, t23.y)
+#undef HGC_MAX
+                        }
+                    }
+                }
+                continue;
+            }
+            // chunk with padding (-1) or out-of-range ids: neighbour by neighbour
+            for (int kk = 0; kk < LPH; kk++) {
+                const int j = __shfl_sync(0xffffffffu, my_j, kk, LPH);
+                const float w = __shfl_sync(0xffffffffu, my_w, kk, LPH);
+                if (j < 0) continue;
+                const bool first = (c0 + kk) == 0;
+#pragma unroll
+                for (int u = 0; u < VPL; u++) {
+                    const int vec = gl + u * LPH;
+                    const float4 f = __ldg(feat + (size_t)j * F4 + (vec < F4 ? vec : 0));
 #define HGC_ACC(comp)                                                           \
     {                                                                           \
-        const float t = __fmul_rn(f[kk][u].comp, w[kk]);                        \
+        const float t = __fmul_rn(f.comp, w);                                   \
         sum[u].comp = __fadd_rn(sum[u].comp, t);                                \
         if (t >= best[u].comp || first) {                                       \
             best[u].comp = t;                                                   \
-            if (WITH_ARG) arg[u].comp = j[kk];                                  \
+            if (WITH_ARG) arg[u].comp = j;                                      \
         }                                                                       \
     }
-                        HGC_ACC(x) HGC_ACC(y) HGC_ACC(z) HGC_ACC(w)
+                    HGC_ACC(x) HGC_ACC(y) HGC_ACC(z) HGC_ACC(w)
 #undef HGC_ACC
-                    }
                 }
             }
         }
@@ -103,10 +173,10 @@ accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restric
                 m.z = __fdiv_rn(sum[u].z, inv_count);
                 m.w = __fdiv_rn(sum[u].w, inv_count);
                 float4 *row = reinterpret_cast<float4 *>(out + (size_t)v * n_out_feat);
-                row[vec] = m;
+                __stcs(row + vec, m);  // results are written once and not read again by this kernel
                 if (mean_and_max) {
-                    row[F4 + vec] = best[u];
-                    if (WITH_ARG) reinterpret_cast<int4 *>(out_arg + (size_t)v * F4 * 4)[vec] = arg[u];
+                    __stcs(row + F4 + vec, best[u]);
+                    if (WITH_ARG) __stcs(reinterpret_cast<int4 *>(out_arg + (size_t)v * F4 * 4) + vec, arg[u]);
                 }
             }
         }
@@ -147,18 +217,17 @@ accumulate_scalar_kernel(const float *__restrict__ weights, const float *__restr
     }
 }
 
-template <int LPH, int VPL>
+template <int LPH, int VPL, int CH, int MINB>
 int launch_vec(bool exp_w, bool with_arg, const float *w, const float *feat, const int *idxs, float *out,
                int *out_arg, int n_vert, int K, int F4, int n_out, bool mm, const int *order,
                float scale, cudaStream_t stream)
 {
-    const int groups_per_block = kAccThreads / LPH;
-    long long blocks = div_up(n_vert, groups_per_block);
+    long long blocks = div_up(n_vert, kAccTile);
     const long long cap = (long long)kNumSMs * 32;
     if (blocks > cap) blocks = cap;
     const float4 *f4 = reinterpret_cast<const float4 *>(feat);
 #define HGC_GO(E, A)                                                                              \
-    accumulate_vec_kernel<LPH, VPL, E, A><<<(int)blocks, kAccThreads, 0, stream>>>(               \
+    accumulate_vec_kernel<LPH, VPL, CH, MINB, E, A><<<(int)blocks, kAccThreads, 0, stream>>>(     \
             w, f4, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale)
     if (exp_w) { if (with_arg) HGC_GO(true, true); else HGC_GO(true, false); }
     else       { if (with_arg) HGC_GO(false, true); else HGC_GO(false, false); }
@@ -194,13 +263,24 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
         return HGC_OK;
     }
     const int F4 = F / 4;
-#define HGC_VEC(L, V) return launch_vec<L, V>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale, stream)
-    if (F4 <= 4) HGC_VEC(4, 1);
-    if (F4 <= 8) HGC_VEC(8, 1);
-    if (F4 <= 16) HGC_VEC(16, 1);
-    if (F4 <= 32) HGC_VEC(32, 1);
-    if (F4 <= 64) HGC_VEC(32, 2);
-    HGC_VEC(32, 4);
+#define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale, stream)
+    if (F4 <= 4) HGC_VEC(4, 1, 4, 3);
+    if (F4 <= 8) HGC_VEC(8, 1, 4, 3);
+    if (F4 <= 16) {
+        int variant = 2;
+        if (const char *e = getenv("HGC_ACC_VARIANT")) variant = atoi(e);  // tuning aid
+        switch (variant) {
+            case 0: HGC_VEC(16, 1, 8, 2);
+            case 1: HGC_VEC(16, 1, 4, 3);
+            case 2: HGC_VEC(16, 1, 4, 4);
+            case 3: HGC_VEC(16, 1, 2, 4);
+            case 4: HGC_VEC(16, 1, 8, 3);
+            default: HGC_VEC(16, 1, 4, 4);
+        }
+    }
+    if (F4 <= 32) HGC_VEC(32, 1, 4, 3);
+    if (F4 <= 64) HGC_VEC(32, 2, 4, 2);
+    HGC_VEC(32, 4, 2, 1);
 #undef HGC_VEC
 }
 
