@@ -266,8 +266,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     K, F = a.neighbours, a.features
-    my_events = [e for e in range(a.events) if e % world == rank] if a.events % world else \
-        list(range(rank * (a.events // world), (rank + 1) * (a.events // world)))
+    from hgcalml_b200.sharding import shard_events
+    first, last = shard_events(np.arange(a.events + 1) * a.hits, world)[rank]
+    my_events = list(range(first, last))
     coords_h, feats_h, rs_h = make_events(a, my_events)
     n = coords_h.shape[0]
     coords_p = torch.from_numpy(coords_h).pin_memory()
