@@ -130,73 +130,9 @@ def _ref_backend():
 
 
 def cpu_path_event(O, backend, coords, feats, row_splits, K, n_threads=1, pool=None):
-    """The reference's CPU path for one batch: wrapper glue in numpy, the ops from the CPU library.
-    With n_threads > 1 the queries of the batch are split over threads: the search uses the op's own
-    `direction` input (0 = may only be a neighbour) to restrict each thread to its slice of queries,
-    AccumulateKnn is called on row slices; both give results identical to a single call."""
-    c = np.ascontiguousarray(coords, np.float32)
-    n = c.shape[0]
-    mbd = min(3, c.shape[1])
-    nb0 = O.default_n_bins(int(row_splits[1]), K, mbd)
-    dbin, binning, nb, bw, nper = O.BinByCoordinates(c[:, :mbd], row_splits, n_bins=nb0, backend=backend)
-    sorting = np.argsort(binning, kind="stable").astype(np.int32)
-    sc, sb, sdb = c[sorting], binning[sorting], dbin[sorting]
-    bb = np.concatenate([np.zeros(1, np.int32), nper]).cumsum().astype(np.int32)
-    if n_threads <= 1:
-        idx_s, dist_s = O.op_binned_select_knn(K, sc, sb, sdb, bb, nb, bw, backend=backend)
-    else:
-        bounds = np.linspace(0, n, n_threads + 1).astype(np.int64)
-        idx_s = np.empty((n, K), np.int32)
-        dist_s = np.empty((n, K), np.float32)
-
-        def knn_slice(t):
-            lo, hi = bounds[t], bounds[t + 1]
-            direction = np.zeros((n,), np.int32)
-            direction[lo:hi] = 3
-            i, d = O.op_binned_select_knn(K, sc, sb, sdb, bb, nb, bw, direction=direction, backend=backend)
-            idx_s[lo:hi] = i[lo:hi]
-            dist_s[lo:hi] = d[lo:hi]
-        list(pool.map(knn_slice, range(n_threads)))
-    idx_r = O.op_index_replacer(idx_s, sorting, backend)
-    idx = np.empty_like(idx_r)
-    dist = np.empty_like(dist_s)
-    idx[sorting] = idx_r
-    dist[sorting] = dist_s
-    dist = np.where(idx < 0, np.float32(0), dist)
-    w = np.exp(-(np.float32(10.) * dist)).astype(np.float32)
-    if n_threads <= 1:
-        out, _ = O.op_accumulate_knn(w, feats, idx, backend=backend)
-    else:
-        bounds = np.linspace(0, n, n_threads + 1).astype(np.int64)
-        out = np.empty((n, 2 * feats.shape[1]), np.float32)
-
-        def acc_slice(t):
-            lo, hi = bounds[t], bounds[t + 1]
-            # rows lo..hi of the batch; indices stay absolute, so features are passed whole
-            o, _ = _accumulate_rows(O, backend, w, feats, idx, lo, hi)
-            out[lo:hi] = o
-        list(pool.map(acc_slice, range(n_threads)))
-    return out
-
-
-def _accumulate_rows(O, backend, w, feats, idx, lo, hi):
-    """AccumulateKnn on rows [lo, hi): the functor takes the row count of distances/indices and only
-    ever indexes features through the neighbour ids, so a row slice is a plain pointer offset."""
-    import ctypes
-    n, k = idx.shape
-    f = feats.shape[1]
-    out = np.zeros((hi - lo, 2 * f), np.float32)
-    maxidx = np.zeros((hi - lo, f), np.int32)
-    fn = O.lib(backend).fn("accumulate_knn")
-    fp, ip = ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)
-    args = [w[lo:hi].ctypes.data_as(fp), feats.ctypes.data_as(fp), idx[lo:hi].ctypes.data_as(ip),
-            out.ctypes.data_as(fp), maxidx.ctypes.data_as(ip), ctypes.c_int(hi - lo), ctypes.c_int(k),
-            ctypes.c_int(f), ctypes.c_int(2 * f)]
-    if backend == "ref":
-        args.append(ctypes.c_int(0))
-    args.append(ctypes.c_int(1))
-    fn(*args)
-    return out, maxidx
+    """The reference's CPU path for one batch (wrapper glue in numpy, ops from the CPU library),
+    optionally with queries / rows spread over threads; see oracle.knn_accumulate_path."""
+    return O.knn_accumulate_path(K, coords, feats, row_splits, n_threads=n_threads, pool=pool, backend=backend)
 
 
 def run_reference_arm(a):

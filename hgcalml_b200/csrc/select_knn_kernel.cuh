@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
 {
     __shared__ knn_key s_buf[kKnnWarps][2 * kWarp];
     __shared__ int s_start[kKnnWarps][kWarp];
-    __shared__ int s_end[kKnnWarps][kWarp];  // inclusive prefix of the short ranges' lengths
+    __shared__ int s_end[kKnnWarps][kWarp];  // inclusive prefix of range lengths / chunk counts
+    __shared__ int s_rbeg[kKnnWarps][kWarp], s_rend[kKnnWarps][kWarp];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = a.K;
@@ -270,7 +271,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
         Q.thr = HGC_KNN_INF_KEY;
         Q.buffered = 0;
         HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0; Q.t_flush = Q.t_offer = 0; const long long t_query0 = clock64());
-        HGC_STAT(unsigned n_boxes = 0; unsigned n_chunks = 0);
+        HGC_STAT(unsigned st_boxes = 0; unsigned st_chunks = 0);
         Q.lane = lane;
         Q.self = i;
         Q.buf = s_buf[warp];
@@ -357,28 +358,50 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                     }
                     shell_in_grid = shell_in_grid || __any_sync(0xffffffffu, slot_in_grid);
 
-                    // ---- long ranges: chunk by chunk, nearest bounding box first ----
-                    unsigned long_mask = __ballot_sync(0xffffffffu, len > a.long_range);
-                    while (long_mask) {
-                        const int src = __ffs(long_mask) - 1;
-                        long_mask &= long_mask - 1;
-                        const int r_begin = __shfl_sync(0xffffffffu, start, src);
-                        const int r_end = r_begin + __shfl_sync(0xffffffffu, len, src);
-                        const int c_last = (r_end - 1) >> 5;
-                        for (int cb0 = r_begin >> 5; cb0 <= c_last; cb0 += kWarp) {
-                            const int chunk = cb0 + lane;
-                            float lb = INFINITY;
-                            if (chunk <= c_last) lb = box_distsq<NV4>(Q.q, a.chunk_lo, a.chunk_hi, (size_t)chunk);
-                            unsigned alive = __ballot_sync(0xffffffffu, chunk <= c_last && lb <= Q.kth());
-                            HGC_STAT(n_boxes += min(c_last - cb0 + 1, kWarp));
-                            while (alive) {
-                                const int cl = __ffs(alive) - 1;
-                                alive &= alive - 1;
-                                // the K-th best may have tightened since the box test
-                                if (__shfl_sync(0xffffffffu, lb, cl) > Q.kth()) continue;
-                                HGC_STAT(n_chunks++);
-                                const int j = ((cb0 + cl) << 5) + lane;
-                                Q.offer(j >= r_begin && j < r_end, j);
+                    // ---- long ranges: their chunks, all rows together, nearest bounding box first ----
+                    const bool is_long = len > a.long_range;
+                    if (__any_sync(0xffffffffu, is_long)) {
+                        const int n_chunks = is_long ? ((start + len - 1) >> 5) - (start >> 5) + 1 : 0;
+                        int cincl = n_chunks;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const int t = __shfl_up_sync(0xffffffffu, cincl, o);
+                            if (lane >= o) cincl += t;
+                        }
+                        const int total_chunks = __shfl_sync(0xffffffffu, cincl, 31);
+                        __syncwarp();
+                        s_start[warp][lane] = (start >> 5) - (cincl - n_chunks);  // chunk = s_start[r] + v
+                        s_end[warp][lane] = cincl;
+                        s_rbeg[warp][lane] = start;
+                        s_rend[warp][lane] = start + len;
+                        __syncwarp();
+                        int r = 0;
+                        for (int v0 = 0; v0 < total_chunks; v0 += kWarp) {
+                            const int v = v0 + lane;
+                            int chunk = 0, r_begin = 0, r_end = 0;
+                            knn_key order_key = HGC_KNN_INF_KEY;
+                            if (v < total_chunks) {
+                                while (v >= s_end[warp][r]) r++;
+                                chunk = s_start[warp][r] + v;
+                                r_begin = s_rbeg[warp][r];
+                                r_end = s_rend[warp][r];
+                                const float lb = box_distsq<NV4>(Q.q, a.chunk_lo, a.chunk_hi, (size_t)chunk);
+                                if (lb <= Q.kth()) order_key = make_key(lb, lane);
+                            }
+                            HGC_STAT(st_boxes += min(total_chunks - v0, kWarp));
+                            const int alive = __popc(__ballot_sync(0xffffffffu, order_key != HGC_KNN_INF_KEY));
+                            if (alive == 0) continue;
+                            order_key = warp_sort(order_key, lane);
+                            for (int n = 0; n < alive; n++) {
+                                const knn_key ok = shfl_key(order_key, n);
+                                if (key_distsq(ok) > Q.kth()) break;  // sorted: the remaining boxes are farther still
+                                const int src = key_index(ok);
+                                const int c = __shfl_sync(0xffffffffu, chunk, src);
+                                const int rb = __shfl_sync(0xffffffffu, r_begin, src);
+                                const int re = __shfl_sync(0xffffffffu, r_end, src);
+                                HGC_STAT(st_chunks++);
+                                const int j = (c << 5) + lane;
+                                Q.offer(j >= rb && j < re, j);
                             }
                         }
                     }
@@ -427,8 +450,8 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
             atomicAdd(&a.stats[1], (unsigned long long)Q.n_offered);
             atomicAdd(&a.stats[2], (unsigned long long)Q.n_accepted);
             atomicAdd(&a.stats[3], (unsigned long long)Q.n_flushes);
-            atomicAdd(&a.stats[4], (unsigned long long)n_boxes);
-            atomicAdd(&a.stats[5], (unsigned long long)n_chunks);
+            atomicAdd(&a.stats[4], (unsigned long long)st_boxes);
+            atomicAdd(&a.stats[5], (unsigned long long)st_chunks);
             atomicAdd(&a.stats[6], (unsigned long long)Q.n_steps);
             atomicAdd(&a.stats[7], (unsigned long long)(clock64() - t_query0));
             atomicAdd(&a.stats[8], (unsigned long long)Q.t_flush);

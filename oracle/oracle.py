@@ -351,6 +351,89 @@ def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_thres
 
 
 # --------------------------------------------------------------------------
+# multi-threaded use of the single-threaded CPU ops (ctypes releases the GIL)
+# --------------------------------------------------------------------------
+def op_binned_select_knn_threaded(K, coords, bin_idx, dim_bin_idx, bin_boundaries, n_bins, bin_width,
+                                  n_threads, pool, backend="port"):
+    """The search op with its queries split over threads.  Each thread calls the unmodified op with
+    the op's own `direction` input set to 0 ("may only be a neighbour") outside its slice of
+    queries and 3 (no restriction) inside, and keeps its slice of the rows: identical to one call."""
+    n = coords.shape[0]
+    bounds = np.linspace(0, n, n_threads + 1).astype(np.int64)
+    idx = np.empty((n, K), np.int32)
+    dist = np.empty((n, K), np.float32)
+
+    def work(t):
+        lo, hi = bounds[t], bounds[t + 1]
+        direction = np.zeros((n,), np.int32)
+        direction[lo:hi] = 3
+        i, d = op_binned_select_knn(K, coords, bin_idx, dim_bin_idx, bin_boundaries, n_bins, bin_width,
+                                    direction=direction, backend=backend)
+        idx[lo:hi] = i[lo:hi]
+        dist[lo:hi] = d[lo:hi]
+    list(pool.map(work, range(n_threads)))
+    return idx, dist
+
+
+def op_accumulate_knn_rows(weights, features, indices, lo, hi, backend="port"):
+    """AccumulateKnn on rows [lo, hi): the functor only reaches features through the neighbour
+    ids, so a row slice of weights / indices / outputs is a plain pointer offset."""
+    k = indices.shape[1]
+    f = features.shape[1]
+    out = np.zeros((hi - lo, 2 * f), np.float32)
+    maxidx = np.zeros((hi - lo, f), np.int32)
+    fn = lib(backend).fn("accumulate_knn")
+    args = [_f(weights[lo:hi]), _f(features), _i(indices[lo:hi]), _f(out), _i(maxidx),
+            c_int(hi - lo), c_int(k), c_int(f), c_int(2 * f)]
+    if backend == "ref":
+        args.append(c_int(0))
+    args.append(c_int(1))
+    fn(*args)
+    return out, maxidx
+
+
+def knn_accumulate_path(K, coords, feats, row_splits, n_threads=1, pool=None, backend="port",
+                        distance_scale=10., return_all=False):
+    """The reference's CPU path for one batch -- BinnedSelectKnn wrapper, exp(-scale*d^2) weights,
+    AccumulateKnn -- optionally with the per-query / per-row work spread over threads."""
+    c = _c32f(coords)
+    feats = _c32f(feats)
+    row_splits = _c32i(row_splits)
+    n = c.shape[0]
+    mbd = min(3, c.shape[1])
+    nb0 = default_n_bins(int(row_splits[1]), K, mbd)
+    dbin, binning, nb, bw, nper = BinByCoordinates(c[:, :mbd], row_splits, n_bins=nb0, backend=backend)
+    sorting = np.argsort(binning, kind="stable").astype(np.int32)
+    sc, sb, sdb = c[sorting], binning[sorting], dbin[sorting]
+    bb = np.concatenate([np.zeros(1, np.int32), nper]).cumsum().astype(np.int32)
+    if n_threads <= 1:
+        idx_s, dist_s = op_binned_select_knn(K, sc, sb, sdb, bb, nb, bw, backend=backend)
+    else:
+        idx_s, dist_s = op_binned_select_knn_threaded(K, sc, sb, sdb, bb, nb, bw, n_threads, pool, backend)
+    idx_r = op_index_replacer(idx_s, sorting, backend)
+    idx = np.empty_like(idx_r)
+    dist = np.empty_like(dist_s)
+    idx[sorting] = idx_r
+    dist[sorting] = dist_s
+    dist = np.where(idx < 0, np.float32(0), dist)
+    w = np.exp(-(np.float32(distance_scale) * dist)).astype(np.float32)
+    if n_threads <= 1:
+        out, maxidx = op_accumulate_knn(w, feats, idx, backend=backend)
+    else:
+        bounds = np.linspace(0, n, n_threads + 1).astype(np.int64)
+        out = np.empty((n, 2 * feats.shape[1]), np.float32)
+        maxidx = np.empty((n, feats.shape[1]), np.int32)
+
+        def work(t):
+            lo, hi = bounds[t], bounds[t + 1]
+            out[lo:hi], maxidx[lo:hi] = op_accumulate_knn_rows(w, feats, idx, lo, hi, backend)
+        list(pool.map(work, range(n_threads)))
+    if return_all:
+        return idx, dist, out, maxidx
+    return out
+
+
+# --------------------------------------------------------------------------
 # parity helpers
 # --------------------------------------------------------------------------
 def canonical_knn(idx, dist):
