@@ -188,17 +188,20 @@ def test_accumulate_knn_vs_checker(cuda, oracle, n, K, F, mm):
         assert np.array_equal(N(ga), ra)
 
 
-def exp_weighted_tolerance(d, feats, idx, ref):
+def exp_weighted_tolerance(d, feats, idx, ref, rows_per_block=4096):
     """1e-5 relative, measured against the size of the summed terms: the mean may cancel to
     something much smaller than its terms, and the weights differ in their last bits (expf on the
     device, float32 exp on the host), so the bound is 1e-5 * max(|ref|, mean_k |w_k f_k|)."""
-    w = np.exp(-d.astype(np.float64))
-    nb = np.where(idx < 0, 0, idx)
-    terms = np.abs(feats[nb].astype(np.float64) * w[:, :, None]) * (idx >= 0)[:, :, None]
-    absmean = terms.mean(axis=1)
     F = feats.shape[1]
-    scale = np.concatenate([absmean, np.abs(ref[:, F:])], axis=1)
-    return 1e-5 * np.maximum(np.abs(ref), scale) + 1e-12
+    tol = np.empty(ref.shape, np.float64)
+    for lo in range(0, len(idx), rows_per_block):
+        hi = min(lo + rows_per_block, len(idx))
+        w = np.exp(-d[lo:hi].astype(np.float64))
+        nb = np.where(idx[lo:hi] < 0, 0, idx[lo:hi])
+        terms = np.abs(feats[nb].astype(np.float64) * w[:, :, None]) * (idx[lo:hi] >= 0)[:, :, None]
+        scale = np.concatenate([terms.mean(axis=1), np.abs(ref[lo:hi, F:])], axis=1)
+        tol[lo:hi] = 1e-5 * np.maximum(np.abs(ref[lo:hi]), scale) + 1e-12
+    return tol
 
 
 @pytest.mark.parametrize("name", ["knn_uniform3d", "knn_showers4d"])
