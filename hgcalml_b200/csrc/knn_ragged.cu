@@ -119,7 +119,7 @@ extern "C" int hgc_binned_select_knn_ragged(
     Carver ws(workspace);
     RaggedBuffers b;
     layout(ws, n_vert, n_coords, p, use_direction != 0, &b);
-    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
+    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, kAlign, stream));
 
     if (int rc = compute_grid(d_coords, n_coords, p.cb, n_coords, n_vert, d_row_splits, n_rs, n_bins, n_neigh,
                               /*pre_normalized=*/0, b.partial, b.grid, stream))

@@ -85,7 +85,12 @@ int launch_select_knn(const KnnScratch &s, int n_coords, const int *bin_idx, con
     a.out_idx = out_idx; a.out_dist = out_dist; a.row_map = row_map; a.id_map = id_map;
     a.n_vert = n_vert; a.K = K; a.n_bboundaries = n_bboundaries; a.tf_compat = tf_compat;
     a.status = status;
+    a.work_counter = status + 16;  // inside the 256 zeroed bytes that start every workspace
     a.long_range = 96;
+    a.fetch = 1;
+    a.blocks_per_sm = 4;
+    if (const char *e = getenv("HGC_KNN_FETCH")) a.fetch = atoi(e);            // tuning aids
+    if (const char *e = getenv("HGC_KNN_BLOCKS_PER_SM")) a.blocks_per_sm = atoi(e);
     if (const char *e = getenv("HGC_KNN_LONG_RANGE")) a.long_range = atoi(e);  // tuning aid
     a.stats = nullptr;
     if (getenv("HGC_KNN_STATS")) {
@@ -152,7 +157,7 @@ extern "C" int hgc_binned_select_knn(
     const size_t need = hgc_binned_select_knn_workspace_bytes(n_vert, n_neigh, n_coords, n_bin_dim);
     if (int rc = check_workspace(workspace, workspace_bytes, need)) return rc;
     Carver ws(workspace);
-    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
+    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, kAlign, stream));
     const KnnScratch s = knn_scratch_layout(ws, n_vert, n_coords);
     if (int rc = pack_points(d_coord, n_coords, nullptr, s, n_vert, stream)) return rc;
     return launch_select_knn(s, n_coords, d_bin_idx, d_dim_bin_idx, d_bin_boundaries, d_n_bins,

@@ -20,8 +20,10 @@ struct KnnArgs {
     const int *id_map;          // output id of bin-sorted hit j (null: j)
     int n_vert, K, n_bboundaries;
     int tf_compat;
+    int fetch, blocks_per_sm;   // queries a warp takes at a time; grid size per SM
     int long_range;             // ranges longer than this are scanned chunk-wise with box tests
     unsigned *status;
+    unsigned *work_counter;     // zeroed before the launch; hands out runs of queries to warps
     unsigned long long *stats;  // optional work counters (tuning aid), null in normal use
 };
 

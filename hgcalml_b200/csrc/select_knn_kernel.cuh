@@ -39,9 +39,12 @@ typedef double knn_key;
 #else
 #define HGC_STAT(x)
 #endif
+#ifndef HGC_KNN_MIN_BLOCKS
+#define HGC_KNN_MIN_BLOCKS 4
+#endif
 constexpr int kKnnWarps = 8;
 constexpr int kKnnThreads = kKnnWarps * kWarp;
-constexpr int kQueriesPerBlock = 64;   // consecutive bin-sorted queries handled by one block
+constexpr int kQueriesPerFetch = 2;    // consecutive bin-sorted queries a warp takes at a time
 
 __device__ __forceinline__ knn_key make_key(float distsq, int j)
 {
@@ -236,7 +239,7 @@ struct Query {
 };
 
 template <int NV4, int L, int CB, bool USE_DIR>
-__global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a)
+__global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_kernel(const KnnArgs a)
 {
     __shared__ knn_key s_buf[kKnnWarps][2 * kWarp];
     __shared__ int s_start[kKnnWarps][kWarp];
@@ -256,10 +259,15 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
     }
     const int bins_per_event = stride[0] * nb[0];
 
-    const int q_begin = blockIdx.x * kQueriesPerBlock;
-    const int q_end = min(q_begin + kQueriesPerBlock, a.n_vert);
-
-    for (int i = q_begin + warp; i < q_end; i += kKnnWarps) {
+    // Warps fetch small runs of consecutive queries from one counter: queries differ a lot in cost
+    // (dense shower vs sparse noise), and a fixed assignment leaves warps idle at the end of a block.
+    for (;;) {
+    int run_begin = 0;
+    if (lane == 0) run_begin = (int)atomicAdd(a.work_counter, (unsigned)a.fetch);
+    run_begin = __shfl_sync(0xffffffffu, run_begin, 0);
+    if (run_begin >= a.n_vert) break;
+    const int run_end = min(run_begin + a.fetch, a.n_vert);
+    for (int i = run_begin; i < run_end; i++) {
         const int out_row = a.row_map ? a.row_map[i] : i;
         const int self_id = a.id_map ? a.id_map[i] : i;
         int *row_idx = a.out_idx + (size_t)out_row * K;
@@ -271,7 +279,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
         Q.thr = HGC_KNN_INF_KEY;
         Q.buffered = 0;
         HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0; Q.t_flush = Q.t_offer = 0; const long long t_query0 = clock64());
-        HGC_STAT(unsigned st_boxes = 0; unsigned st_chunks = 0);
+        HGC_STAT(unsigned st_boxes = 0; unsigned st_chunks = 0; long long t_enum = 0; long long t_box = 0; long long t_out = 0);
         Q.lane = lane;
         Q.self = i;
         Q.buf = s_buf[warp];
@@ -315,6 +323,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                 // pass) or the two end bins of the row.  Cells are visited starting at the query's
                 // own row, which tightens the K-th best early.
                 for (int base = 0; base < 2 * cells; base += kWarp) {
+                    HGC_STAT(const long long te0 = clock64());
                     const int slot = base + lane;
                     int start = 0, len = 0;
                     bool slot_in_grid = false;
@@ -358,6 +367,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                     }
                     shell_in_grid = shell_in_grid || __any_sync(0xffffffffu, slot_in_grid);
 
+                    HGC_STAT(t_enum += clock64() - te0);
                     // ---- long ranges: their chunks, all rows together, nearest bounding box first ----
                     const bool is_long = len > a.long_range;
                     if (__any_sync(0xffffffffu, is_long)) {
@@ -377,6 +387,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                         __syncwarp();
                         int r = 0;
                         for (int v0 = 0; v0 < total_chunks; v0 += kWarp) {
+                            HGC_STAT(const long long tb0 = clock64());
                             const int v = v0 + lane;
                             int chunk = 0, r_begin = 0, r_end = 0;
                             knn_key order_key = HGC_KNN_INF_KEY;
@@ -392,6 +403,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                             const int alive = __popc(__ballot_sync(0xffffffffu, order_key != HGC_KNN_INF_KEY));
                             if (alive == 0) continue;
                             order_key = warp_sort(order_key, lane);
+                            HGC_STAT(t_box += clock64() - tb0);
                             for (int n = 0; n < alive; n++) {
                                 const knn_key ok = shfl_key(order_key, n);
                                 if (key_distsq(ok) > Q.kth()) break;  // sorted: the remaining boxes are farther still
@@ -444,20 +456,7 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
             }
         }
 
-#ifdef HGC_KNN_STATS
-        if (a.stats && lane == 0) {
-            atomicAdd(&a.stats[0], 1ull);
-            atomicAdd(&a.stats[1], (unsigned long long)Q.n_offered);
-            atomicAdd(&a.stats[2], (unsigned long long)Q.n_accepted);
-            atomicAdd(&a.stats[3], (unsigned long long)Q.n_flushes);
-            atomicAdd(&a.stats[4], (unsigned long long)st_boxes);
-            atomicAdd(&a.stats[5], (unsigned long long)st_chunks);
-            atomicAdd(&a.stats[6], (unsigned long long)Q.n_steps);
-            atomicAdd(&a.stats[7], (unsigned long long)(clock64() - t_query0));
-            atomicAdd(&a.stats[8], (unsigned long long)Q.t_flush);
-            atomicAdd(&a.stats[9], (unsigned long long)Q.t_offer);
-        }
-#endif
+        HGC_STAT(const long long to0 = clock64());
         // write the row: slot 0 = the query, slots 1.. = list ranks 0.. (ascending)
         const int pad = a.tf_compat ? self_id : -1;
         if (lane == 0) { row_idx[0] = self_id; row_dist[0] = 0.f; }
@@ -477,13 +476,32 @@ __global__ void __launch_bounds__(kKnnThreads) select_knn_kernel(const KnnArgs a
                 row_dist[slot] = ds;
             }
         }
+#ifdef HGC_KNN_STATS
+        t_out = clock64() - to0;
+        if (a.stats && lane == 0) {
+            atomicAdd(&a.stats[0], 1ull);
+            atomicAdd(&a.stats[1], (unsigned long long)Q.n_offered);
+            atomicAdd(&a.stats[2], (unsigned long long)Q.n_accepted);
+            atomicAdd(&a.stats[3], (unsigned long long)Q.n_flushes);
+            atomicAdd(&a.stats[4], (unsigned long long)st_boxes);
+            atomicAdd(&a.stats[5], (unsigned long long)st_chunks);
+            atomicAdd(&a.stats[6], (unsigned long long)Q.n_steps);
+            atomicAdd(&a.stats[7], (unsigned long long)(to0 - t_query0));
+            atomicAdd(&a.stats[8], (unsigned long long)Q.t_flush);
+            atomicAdd(&a.stats[9], (unsigned long long)Q.t_offer);
+            atomicAdd(&a.stats[10], (unsigned long long)t_enum);
+            atomicAdd(&a.stats[11], (unsigned long long)t_box);
+            atomicAdd(&a.stats[12], (unsigned long long)t_out);
+        }
+#endif
+    }
     }
 }
 
 template <int NV4, int L, int CB>
 int launch_knn3(const KnnArgs &a, bool use_dir, cudaStream_t stream)
 {
-    const int blocks = div_up(a.n_vert, kQueriesPerBlock);
+    const int blocks = min(div_up(a.n_vert, kKnnWarps * a.fetch), kNumSMs * a.blocks_per_sm);
     if (use_dir) select_knn_kernel<NV4, L, CB, true><<<blocks, kKnnThreads, 0, stream>>>(a);
     else         select_knn_kernel<NV4, L, CB, false><<<blocks, kKnnThreads, 0, stream>>>(a);
     HGC_LAUNCH_CHECK();

@@ -64,7 +64,7 @@ extern "C" int hgc_binned_select_knn_static(
     if (int rc = scratch_for_current_device(&scratch)) return rc;
     Carver ws(scratch);
     // the status word must start at zero; packed points and boxes are rewritten for all n_vert hits
-    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, sizeof(unsigned), stream));
+    HGC_CUDA_TRY(cudaMemsetAsync(ws.status(), 0, kAlign, stream));
     const KnnScratch s = knn_scratch_layout(ws, n_vert, n_coords);
     if (int rc = pack_points(d_coord, n_coords, nullptr, s, n_vert, stream)) return rc;
     return launch_select_knn(s, n_coords, d_bin_idx, d_dim_bin_idx, d_bin_boundaries, d_n_bins,
