@@ -32,6 +32,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "hits/sec for BinnedSelectKnn+AccumulateKnn at 200k-hit events"
 UNIT = "hits/s"
+# DRAM traffic per hit of the two main kernels at K = F = 64, 4 coordinates, from the ncu capture
+# summarised in profiles/select_knn_and_accumulate_2events_full.md (traffic grows with the hits).
+ACC_DRAM_BYTES_PER_HIT = 1972
+KNN_DRAM_BYTES_PER_HIT = 408
 
 
 def parse():
@@ -299,12 +303,14 @@ def main():
             knn_bytes = n * (4 * 4 + 4 + 4 * 4 + 8 * K)
             acc = {"kernel": "accumulate_vec_kernel", "bound": "hbm",
                    "achieved": acc_bytes / (kernel_times["accumulate_ms"] * 1e-3) / 1e9, "peak": hbm_peak,
-                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": None,
+                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * ACC_DRAM_BYTES_PER_HIT),
+                   "traffic_source": "ncu dram__bytes_read+write of a 400k-hit launch, scaled by hits",
                    "ms_per_launch": kernel_times["accumulate_ms"], "algorithmic_bytes": acc_bytes}
             acc["frac"] = acc["achieved"] / hbm_peak
             knn = {"kernel": "select_knn_kernel", "bound": "hbm",
                    "achieved": knn_bytes / (kernel_times["select_knn_ms"] * 1e-3) / 1e9, "peak": hbm_peak,
-                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": None,
+                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * KNN_DRAM_BYTES_PER_HIT),
+                   "traffic_source": "ncu dram__bytes_read+write of a 400k-hit launch, scaled by hits",
                    "ms_per_launch": kernel_times["select_knn_ms"], "algorithmic_bytes": knn_bytes,
                    "note": "the search is bound by FP32 issue and shuffles, not by HBM; the HBM figure is "
                            "reported because it is the dominant kernel by time"}
