@@ -303,13 +303,13 @@ def main():
             knn_bytes = n * (4 * 4 + 4 + 4 * 4 + 8 * K)
             acc = {"kernel": "accumulate_vec_kernel", "bound": "hbm",
                    "achieved": acc_bytes / (kernel_times["accumulate_ms"] * 1e-3) / 1e9, "peak": hbm_peak,
-                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * ACC_DRAM_BYTES_PER_HIT),
+                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * ACC_DRAM_BYTES_PER_HIT) if (K, F) == (64, 64) else None,
                    "traffic_source": "ncu dram__bytes_read+write of a 400k-hit launch, scaled by hits",
                    "ms_per_launch": kernel_times["accumulate_ms"], "algorithmic_bytes": acc_bytes}
             acc["frac"] = acc["achieved"] / hbm_peak
             knn = {"kernel": "select_knn_kernel", "bound": "hbm",
                    "achieved": knn_bytes / (kernel_times["select_knn_ms"] * 1e-3) / 1e9, "peak": hbm_peak,
-                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * KNN_DRAM_BYTES_PER_HIT),
+                   "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * KNN_DRAM_BYTES_PER_HIT) if (K, F) == (64, 64) else None,
                    "traffic_source": "ncu dram__bytes_read+write of a 400k-hit launch, scaled by hits",
                    "ms_per_launch": kernel_times["select_knn_ms"], "algorithmic_bytes": knn_bytes,
                    "note": "the search is bound by FP32 issue and shuffles, not by HBM; the HBM figure is "
