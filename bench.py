@@ -73,7 +73,7 @@ def make_events(a, event_ids):
 # ------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -88,11 +88,14 @@ class ClockSampler:
             self.path = f.name
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+                 "--format=csv,noheader,nounits", "-lms", "20"], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Samples taken between the two wall-clock times (all of them when none fall inside: the
+        sampler runs from the warm-up on, so those are under the same load)."""
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -101,27 +104,30 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         try:
             for line in open(self.path):
                 c = [x.strip() for x in line.split(",")]
                 if len(c) < 9:
                     continue
                 try:
-                    sm.append(float(c[1]))
-                    mx.append(float(c[2]))
+                    ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(c[1]), float(c[2]), c[5:9]))
                 except ValueError:
                     continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                   c[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
-                       samples=len(sm))
+        inside = [r for r in rows if t_begin is not None and t_begin <= r[0] <= t_end]
+        use = inside or rows
+        reasons = set()
+        for r in use:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if use:
+            out.update(sm_mhz=float(np.median([r[1] for r in use])), sm_max_mhz=float(max(r[2] for r in use)),
+                       reasons=sorted(reasons), samples=len(use), samples_in_timed_region=len(inside))
         return out
 
 
@@ -231,12 +237,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(a.warmup, 1)):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(a.warmup, 1)):
+        step()
+    barrier()
+    t_begin = time.time()
     launches0 = _capi.lib.hgc_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -246,7 +253,7 @@ def main():
     barrier()
     ms = ev0.elapsed_time(ev1)
     launches = _capi.lib.hgc_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, time.time()) if rank == 0 else None
 
     kernel_times = None
     if rank == 0 and not a.no_kernel_times:

@@ -8,7 +8,6 @@
 // multiply and add, which makes the mean bit-identical to the CPU op
 // (modules/compiled/accumulate_knn_kernel.cc:48-81); the max is reset by slot 0 and later slots win
 // ties, as there.
-#include <cstdlib>
 #include "common.cuh"
 
 namespace hgc {
@@ -266,18 +265,9 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
 #define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale, stream)
     if (F4 <= 4) HGC_VEC(4, 1, 4, 3);
     if (F4 <= 8) HGC_VEC(8, 1, 4, 3);
-    if (F4 <= 16) {
-        int variant = 2;
-        if (const char *e = getenv("HGC_ACC_VARIANT")) variant = atoi(e);  // tuning aid
-        switch (variant) {
-            case 0: HGC_VEC(16, 1, 8, 2);
-            case 1: HGC_VEC(16, 1, 4, 3);
-            case 2: HGC_VEC(16, 1, 4, 4);
-            case 3: HGC_VEC(16, 1, 2, 4);
-            case 4: HGC_VEC(16, 1, 8, 3);
-            default: HGC_VEC(16, 1, 4, 4);
-        }
-    }
+    // F = 64: 16 lanes per hit, 4 rows in flight, 64 registers (4 blocks per SM) measured best of
+    // {8 rows / 2 blocks, 4 / 3, 4 / 4, 2 / 4, 8 / 3}
+    if (F4 <= 16) HGC_VEC(16, 1, 4, 4);
     if (F4 <= 32) HGC_VEC(32, 1, 4, 3);
     if (F4 <= 64) HGC_VEC(32, 2, 4, 2);
     HGC_VEC(32, 4, 2, 1);

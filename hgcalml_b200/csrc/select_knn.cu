@@ -1,14 +1,15 @@
 // BinnedSelectKnn: host side of the search (packing, chunk bounding boxes, dispatch) and the
 // op-level C entry.  The search kernel itself is in select_knn_kernel.cuh.
-#include <cstdlib>
 #include "common.cuh"
 #include "select_knn.cuh"
 
 namespace hgc {
 namespace {
 
-// work counters of the search kernel, filled only while HGC_KNN_STATS is set in the environment
+#ifdef HGC_KNN_STATS
+// work counters of the search kernel (instrumented builds only: make EXTRA=-DHGC_KNN_STATS)
 __device__ unsigned long long g_knn_stats[16];
+#endif
 
 // [n_vert, n_coords] floats (optionally gathered through perm) -> zero-padded float4 records
 __global__ void pack_points_kernel(const float *__restrict__ coords, int n_coords, int nv4,
@@ -89,14 +90,13 @@ int launch_select_knn(const KnnScratch &s, int n_coords, const int *bin_idx, con
     a.long_range = 96;
     a.fetch = 1;
     a.blocks_per_sm = 4;
-    if (const char *e = getenv("HGC_KNN_FETCH")) a.fetch = atoi(e);            // tuning aids
-    if (const char *e = getenv("HGC_KNN_BLOCKS_PER_SM")) a.blocks_per_sm = atoi(e);
-    if (const char *e = getenv("HGC_KNN_LONG_RANGE")) a.long_range = atoi(e);  // tuning aid
     a.stats = nullptr;
-    if (getenv("HGC_KNN_STATS")) {
+#ifdef HGC_KNN_STATS
+    {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_knn_stats) == cudaSuccess) a.stats = static_cast<unsigned long long *>(p);
     }
+#endif
     switch (knn_nv4(n_coords)) {
         case 1: return launch_knn_nv<1>(a, n_bin_dim, use_dir, stream);
         case 2: return launch_knn_nv<2>(a, n_bin_dim, use_dir, stream);
@@ -110,6 +110,7 @@ int launch_select_knn(const KnnScratch &s, int n_coords, const int *bin_idx, con
 
 using namespace hgc;
 
+#ifdef HGC_KNN_STATS
 // Tuning aid: copies the search kernel's work counters (queries, candidates offered, accepted,
 // list merges, boxes tested, chunks scanned, steps, then cycles: per query, in merges, in candidate
 // steps; filled only by a build with -DHGC_KNN_STATS) to the host and clears them.
@@ -121,6 +122,7 @@ extern "C" int hgc_debug_knn_stats(unsigned long long *out16)
     HGC_CUDA_TRY(cudaMemcpyToSymbol(g_knn_stats, zero, sizeof(zero)));
     return HGC_OK;
 }
+#endif
 
 namespace {
 struct SizerW {

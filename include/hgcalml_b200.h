@@ -14,7 +14,8 @@
  *    Problems that only the device can see (an index outside its table, a bin outside the
  *    grid, an iteration cap reached) set a status word in the workspace, which
  *    hgc_workspace_status() reads back.
- *  - Re-entrant: no global mutable state; concurrent calls need distinct workspaces.
+ *  - Re-entrant: the only global state is a statistics counter of kernel launches; concurrent
+ *    calls need distinct workspaces.
  *
  * The paths named in the comments are relative to the cms-pepr/HGCalML repository.
  */
