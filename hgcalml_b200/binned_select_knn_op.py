@@ -81,3 +81,39 @@ def BinnedSelectKnn(K: int, coords, row_splits, direction=None, n_bins=None, max
     if return_sorting:
         return idx, dist, sorting
     return idx, dist
+
+
+def SelectKnnGrad(grad_distances, indices, distances, coordinates):
+    """The registered op ``SelectKnnGrad`` (modules/compiled/select_knn_grad_module.cc), which the
+    reference attaches as the gradient of ``BinnedSelectKnn`` (modules/binned_select_knn_op.py:107-118):
+    gradient of the squared neighbour distances with respect to the coordinates, ``[N, C]``."""
+    C.require_cuda(grad_distances, indices, coordinates)
+    g, idx, coords = C.f32(grad_distances), C.i32(indices), C.f32(coordinates)
+    d = None if distances is None else C.f32(distances)
+    n, k = idx.shape
+    out = torch.empty_like(coords)
+    ws = C.workspace(C.lib.hgc_knn_grad_workspace_bytes(n, k), coords.device)
+    C.check(C.lib.hgc_select_knn_grad(C.ptr(g), C.ptr(idx), C.ptr(d), C.ptr(coords), C.ptr(out),
+                                      n, k, coords.shape[1], C.ptr(ws), ws.numel(), C.stream_of(coords)),
+            "SelectKnnGrad")
+    return out
+
+
+class _BinnedSelectKnnFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, coords, row_splits, K, n_bins, max_bin_dims, tf_compatible):
+        idx, dist = BinnedSelectKnn(K, coords, row_splits, n_bins=n_bins, max_bin_dims=max_bin_dims,
+                                    tf_compatible=tf_compatible)
+        ctx.save_for_backward(coords, idx, dist)
+        ctx.mark_non_differentiable(idx)
+        return idx, dist
+
+    @staticmethod
+    def backward(ctx, _grad_idx, grad_dist):
+        coords, idx, dist = ctx.saved_tensors
+        return SelectKnnGrad(grad_dist.contiguous(), idx, dist, coords), None, None, None, None, None
+
+
+def BinnedSelectKnnDifferentiable(K, coords, row_splits, n_bins=None, max_bin_dims=3, tf_compatible=False):
+    """``BinnedSelectKnn`` whose squared distances carry the reference's gradient to the coordinates."""
+    return _BinnedSelectKnnFunction.apply(coords, row_splits, K, n_bins, max_bin_dims, tf_compatible)

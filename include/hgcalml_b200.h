@@ -200,6 +200,39 @@ int hgc_binned_assign_to_condensates(
         const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, int assign_by_max_beta,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Backward ops (registered as the gradients of AccumulateKnn and BinnedSelectKnn:
+ * modules/accknn_op.py:71-90, modules/binned_select_knn_op.py:107-118).
+ *
+ * AccumulateKnnGrad -- replaces AccumulateKnnGradOpFunctor
+ * (modules/compiled/accumulate_knn_grad_kernel.h:11-34; argument order as there).
+ * d_grad_from_out_features [n_vert, n_grad_from_out_feat] with n_grad_from_out_feat = 2*n_feat
+ * ([d mean | d max]) when mean_and_max, else n_feat; d_distances = the forward op's weights
+ * [n_vert, n_neigh]; d_feat [n_vert, n_feat]; d_max_feat_indices [n_vert, n_feat] (forward output);
+ * d_neigh_indices [n_vert, n_neigh].  Outputs d_out_grad_distances [n_vert, n_neigh] (gradient
+ * w.r.t. the weights) and d_out_grad_features [n_vert, n_feat].  No atomics: contributions to a
+ * hit are summed in (source hit, slot) order, which is the order of the reference's CPU loop.
+ *
+ * SelectKnnGrad -- replaces SelectKnnGradOpFunctor
+ * (modules/compiled/select_knn_grad_kernel.h:15-31): gradient of the squared distances w.r.t. the
+ * coordinates, d_grad_coord [n_vert, n_coords]; d_dist is accepted and not read, as in the
+ * reference.  Deterministic for the same reason.
+ *
+ * Both take a workspace of hgc_knn_grad_workspace_bytes (about 24 bytes per (hit, slot) pair) and
+ * need n_vert * n_neigh < 2^31.
+ * ------------------------------------------------------------------------------------- */
+size_t hgc_knn_grad_workspace_bytes(int n_vert, int n_neigh);
+int hgc_accumulate_knn_grad(
+        const float *d_grad_from_out_features, const float *d_distances, const float *d_feat,
+        const int *d_max_feat_indices, const int *d_neigh_indices,
+        float *d_out_grad_distances, float *d_out_grad_features,
+        int n_vert, int n_neigh, int n_feat, int n_grad_from_out_feat, int n_moments, int mean_and_max,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+int hgc_select_knn_grad(
+        const float *d_grad_dist, const int *d_indices, const float *d_dist, const float *d_coord,
+        float *d_grad_coord, int n_vert, int n_neigh, int n_coords,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

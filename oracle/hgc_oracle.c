@@ -341,3 +341,104 @@ int oracle_binned_assign_to_condensates(
     free(centre);
     return 0;
 }
+
+/* ------------------------------------------------------------------------
+ * AccumulateKnnGrad
+ * restates modules/compiled/accumulate_knn_grad_kernel.cc:25-163.
+ * Feature gradient: every (hit i, slot k) with neighbour m adds
+ *   (g[i,f] / K) * w[i,k]  +  [m == arg-max neighbour of (i,f)] * gmax[i,f] * w[i,k]
+ * to grad_feat[m,f]; when the arg-max neighbour is the hit itself only its first
+ * occurrence in the row counts.  Contributions arrive in (i, k) order.
+ * Weight gradient: grad_w[i,k] = (sum_f g[i,f] * feat[m,f]) * (1/K in double)
+ *   + sum_f [m == arg-max neighbour of (i,f)] * gmax[i,f] * feat[m,f].
+ * ---------------------------------------------------------------------- */
+void oracle_accumulate_knn_grad(
+        const float *grad_out, const float *weights, const float *feat,
+        const int *max_idx, const int *nidx,
+        float *grad_weights, float *grad_feat,
+        int n_vert, int n_neigh, int n_feat, int n_grad_out, int mean_and_max)
+{
+    for (size_t t = 0; t < (size_t)n_vert * n_feat; t++) grad_feat[t] = 0.f;
+
+    for (int i = 0; i < n_vert; i++) {
+        for (int f = 0; f < n_feat; f++) {
+            const float g = grad_out[(size_t)i * n_grad_out + f];
+            float gmax = 0.f;
+            int amax = -1;
+            if (mean_and_max) {
+                gmax = grad_out[(size_t)i * n_grad_out + n_feat + f];
+                amax = max_idx[(size_t)i * n_feat + f];
+            }
+            int self_seen = 0;
+            for (int k = 0; k < n_neigh; k++) {
+                const int m = nidx[(size_t)i * n_neigh + k];
+                if (m < 0) continue;
+                const float w = weights[(size_t)i * n_neigh + k];
+                const float mean_part = g / (float)n_neigh * w;
+                float max_part = 0.f;
+                if (m == amax) {
+                    if (m != i) max_part = gmax * w;
+                    else if (!self_seen) { max_part = gmax * w; self_seen = 1; }
+                }
+                grad_feat[(size_t)m * n_feat + f] += mean_part + max_part;
+            }
+        }
+    }
+
+    for (int i = 0; i < n_vert; i++) {
+        for (int k = 0; k < n_neigh; k++) {
+            const int m = nidx[(size_t)i * n_neigh + k];
+            if (m < 0) { grad_weights[(size_t)i * n_neigh + k] = 0.f; continue; }
+            float mean_part = 0.f, max_part = 0.f;
+            for (int f = 0; f < n_feat; f++) {
+                const float g = grad_out[(size_t)i * n_grad_out + f];
+                const float x = feat[(size_t)m * n_feat + f];
+                mean_part += g * x * 1.f;
+                if (mean_and_max && m == max_idx[(size_t)i * n_feat + f])
+                    max_part += grad_out[(size_t)i * n_grad_out + n_feat + f] * x * 1.f;
+            }
+            mean_part *= 1. / (float)n_neigh;
+            grad_weights[(size_t)i * n_neigh + k] = mean_part + max_part;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------
+ * SelectKnnGrad
+ * The reference's CPU functor for this op is empty
+ * (modules/compiled/select_knn_grad_kernel.cc:24-42); this restates its GPU kernels
+ * (modules/compiled/select_knn_grad_kernel.cu.cc:81-165):
+ *   grad_x[i,c]  = - sum_k 2 * g[i,k] * (x[m,c] - x[i,c])          (accumulated in the reference's mixed
+ *                                                                  float/double arithmetic, k ascending)
+ *   grad_x[m,c] +=   (float)(2 * g[i,k] * (x[m,c] - x[i,c]))       for every (i,k) with neighbour m.
+ * The reference adds the second part with atomics in no fixed order; here it is added in (i, k) order.
+ * PARITY UNPINNED: no reference CPU code exists to run; checked against the analytic gradient instead.
+ * ---------------------------------------------------------------------- */
+void oracle_select_knn_grad(
+        const float *grad_dist, const int *nidx, const float *coord, float *grad_coord,
+        int n_vert, int n_neigh, int n_coords)
+{
+    for (int i = 0; i < n_vert; i++)
+        for (int c = 0; c < n_coords; c++) {
+            const float xi = coord[(size_t)i * n_coords + c];
+            float self = 0.f;
+            for (int k = 0; k < n_neigh; k++) {
+                const int m = nidx[(size_t)i * n_neigh + k];
+                if (m < 0 || m >= n_vert) continue;
+                const float g = grad_dist[(size_t)i * n_neigh + k];
+                const float xm = coord[(size_t)m * n_coords + c];
+                self -= 2. * g * (xm - xi);
+            }
+            grad_coord[(size_t)i * n_coords + c] = self;
+        }
+    for (int i = 0; i < n_vert; i++)
+        for (int k = 0; k < n_neigh; k++) {
+            const int m = nidx[(size_t)i * n_neigh + k];
+            if (m < 0 || m >= n_vert) continue;
+            const float g = grad_dist[(size_t)i * n_neigh + k];
+            for (int c = 0; c < n_coords; c++) {
+                const float add = 2. * g * (coord[(size_t)m * n_coords + c] - coord[(size_t)i * n_coords + c]);
+                grad_coord[(size_t)m * n_coords + c] += add;
+            }
+        }
+}

@@ -164,6 +164,37 @@ def op_accumulate_knn(weights, features, indices, mean_and_max=True, backend="po
     return out, maxidx
 
 
+def op_accumulate_knn_grad(grad_out, weights, features, indices, max_idx, backend="port"):
+    """Functor of accumulate_knn_grad_kernel.cc:166-221. Returns (grad_weights [N,K], grad_features [N,F])."""
+    grad_out = _c32f(grad_out)
+    weights = _c32f(weights)
+    features = _c32f(features)
+    indices = _c32i(indices)
+    n, k = indices.shape
+    f = features.shape[1]
+    mean_and_max = grad_out.shape[1] > f  # the op detects it the same way (accumulate_knn_grad_kernel.cc:246)
+    max_idx = _c32i(max_idx) if max_idx is not None else np.zeros((n, f), np.int32)
+    gw = np.zeros((n, k), np.float32)
+    gf = np.zeros((n, f), np.float32)
+    lib(backend).fn("accumulate_knn_grad")(
+        _f(grad_out), _f(weights), _f(features), _i(max_idx), _i(indices), _f(gw), _f(gf),
+        c_int(n), c_int(k), c_int(f), c_int(grad_out.shape[1]), c_int(int(mean_and_max)))
+    return gw, gf
+
+
+def op_select_knn_grad(grad_dist, indices, coords):
+    """Restatement of the reference's GPU kernels for SelectKnnGrad (its CPU functor is empty).
+    Only the plain-C back end has it.  Returns grad_coords [N,C]."""
+    grad_dist = _c32f(grad_dist)
+    indices = _c32i(indices)
+    coords = _c32f(coords)
+    n, k = indices.shape
+    out = np.zeros_like(coords)
+    lib("port").fn("select_knn_grad")(_f(grad_dist), _i(indices), _f(coords), _f(out),
+                                      c_int(n), c_int(k), c_int(coords.shape[1]))
+    return out
+
+
 def op_binned_assign_to_condensates(ccoords, dist, beta, mask, bins_flat, bin_splits,
                                     indices_to_filtered, original_indices_h, row_splits, n_bins,
                                     bin_width, ccoords_h, dist_h, beta_h, mask_h, row_splits_h,

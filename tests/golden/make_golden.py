@@ -63,6 +63,22 @@ def main():
                                 is_cond=out[3], n_condensates=out[4])
             print(name, "condensates", out[4].tolist(), "noise", int((out[0] < 0).sum()))
 
+    # AccumulateKnnGrad on the neighbour rows of a golden kNN case (padding and repeated self included)
+    g = dict(np.load(os.path.join(OUT, "knn_showers4d_tfcompat.npz")))
+    g2 = dict(np.load(os.path.join(OUT, "knn_showers4d.npz")))
+    for tag, case, base in (("tfcompat", g, "knn_showers4d_tfcompat"), ("padded", g2, "knn_showers4d")):
+        w = np.exp(-(np.float32(10.) * case["dist"])).astype(np.float32)
+        rng = np.random.default_rng(11)
+        for mm in (True, False):
+            out, maxidx = O.op_accumulate_knn(w, case["feats"], case["idx"], mean_and_max=mm, backend=BACKEND)
+            grad_out = rng.standard_normal(out.shape, dtype=np.float32)
+            gw, gf = O.op_accumulate_knn_grad(grad_out, w, case["feats"], case["idx"], maxidx, backend=BACKEND)
+            name = f"accgrad_{tag}_{'meanmax' if mm else 'mean'}"
+            # features and neighbour indices are those of the base case file
+            np.savez_compressed(os.path.join(OUT, name + ".npz"), base=np.array(base), weights=w,
+                                maxidx=maxidx, grad_out=grad_out, grad_weights=gw, grad_feats=gf)
+            print(name, gw.shape, gf.shape)
+
     # bin_by_coordinates op outputs
     c, _, rs = synth.shower_batch([400, 0, 650], dims=3, n_feat=1, seed=77)
     binass, flat, nb, bw, nper = O.BinByCoordinates(c, rs, n_bins=6, backend=BACKEND)

@@ -338,3 +338,70 @@ def test_host_pipeline_matches_direct_calls(cuda):
         idx, d2 = BinnedSelectKnn(K, T(c, cuda), T(rs, cuda))
         ref, _ = AccumulateKnn(d2, T(f, cuda), idx, distance_scale=10.)
         assert torch.equal(out, ref.cpu())
+
+
+# ------------------------------------------------------------------ backward ops
+@pytest.mark.parametrize("name", [f"accgrad_{t}_{m}" for t in ("tfcompat", "padded") for m in ("meanmax", "mean")])
+def test_accumulate_knn_grad_golden(cuda, name):
+    """Bit-identical to the reference's CPU op: contributions are summed in its (hit, slot) order."""
+    from hgcalml_b200.accknn_op import AccumulateKnnGrad
+    g = load_golden(name)
+    gw, gf = AccumulateKnnGrad(T(g["grad_out"], cuda), T(g["weights"], cuda), T(g["feats"], cuda),
+                               T(g["idx"], cuda), T(g["maxidx"], cuda))
+    assert np.array_equal(bits(N(gw)), bits(g["grad_weights"]))
+    assert np.array_equal(bits(N(gf)), bits(g["grad_feats"]))
+
+
+@pytest.mark.parametrize("n,K,F,mm", [(20000, 64, 64, True), (5000, 16, 32, False), (3000, 9, 10, True)])
+def test_accumulate_knn_grad_vs_checker(cuda, oracle, n, K, F, mm):
+    from hgcalml_b200.accknn_op import AccumulateKnnGrad, AccumulateLinKnn
+    rng = np.random.default_rng(n + K)
+    feat = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.random((n, K), dtype=np.float32)
+    idx = rng.integers(0, n, (n, K)).astype(np.int32)
+    idx[:, 0] = np.arange(n)
+    idx[np.arange(K)[None] >= rng.integers(1, K + 1, n)[:, None]] = -1
+    idx[::5, 1] = np.arange(n)[::5]  # the hit itself a second time
+    out, maxidx = AccumulateLinKnn(T(w, cuda), T(feat, cuda), T(idx, cuda), mean_and_max=mm)
+    grad_out = rng.standard_normal(tuple(out.shape), dtype=np.float32)
+    rw, rf = oracle.op_accumulate_knn_grad(grad_out, w, feat, idx, N(maxidx))
+    gw, gf = AccumulateKnnGrad(T(grad_out, cuda), T(w, cuda), T(feat, cuda), T(idx, cuda), maxidx)
+    assert np.array_equal(bits(N(gw)), bits(rw))
+    assert np.array_equal(bits(N(gf)), bits(rf))
+    gw2, gf2 = AccumulateKnnGrad(T(grad_out, cuda), T(w, cuda), T(feat, cuda), T(idx, cuda), maxidx)
+    assert torch.equal(gw, gw2) and torch.equal(gf, gf2)  # no atomics: run-to-run identical
+
+
+def test_select_knn_grad_vs_checker(cuda, oracle):
+    from hgcalml_b200.binned_select_knn_op import SelectKnnGrad
+    g = load_golden("knn_showers4d")
+    gd = np.random.default_rng(5).standard_normal(g["idx"].shape).astype(np.float32)
+    ref = oracle.op_select_knn_grad(gd, g["idx"], g["coords"])
+    got = SelectKnnGrad(T(gd, cuda), T(g["idx"], cuda), T(g["dist"], cuda), T(g["coords"], cuda))
+    assert np.array_equal(bits(N(got)), bits(ref))
+
+
+def test_autograd_through_the_neighbour_path(cuda):
+    """torch autograd through BinnedSelectKnn -> exp(-10 d^2) -> AccumulateKnn agrees with the same
+    graph written with plain torch ops (float64) on the library's neighbour indices."""
+    from hgcalml_b200.binned_select_knn_op import BinnedSelectKnnDifferentiable
+    from hgcalml_b200.accknn_op import AccumulateKnnDifferentiable
+    c, f, rs = synth.shower_batch([1500, 700], dims=4, n_feat=8, seed=12)
+    K = 10
+    coords = T(c, cuda).requires_grad_(True)
+    feats = T(f, cuda).requires_grad_(True)
+    idx, d2 = BinnedSelectKnnDifferentiable(K, coords, T(rs, cuda))
+    out, _ = AccumulateKnnDifferentiable(10. * d2, feats, idx)
+    proj = torch.as_tensor(np.random.default_rng(1).standard_normal(tuple(out.shape)), device=cuda, dtype=torch.float32)
+    (out * proj).sum().backward()
+
+    c64 = T(c, cuda).double().requires_grad_(True)
+    f64 = T(f, cuda).double().requires_grad_(True)
+    nb = idx.long()
+    d2_ref = ((c64[:, None, :] - c64[nb]) ** 2).sum(-1)
+    wf = torch.exp(-10. * d2_ref)[:, :, None] * f64[nb]
+    out_ref = torch.cat([wf.mean(1), wf.max(1).values], dim=1)
+    (out_ref * proj.double()).sum().backward()
+    assert torch.allclose(out.double(), out_ref, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(feats.grad.double(), f64.grad, rtol=1e-3, atol=1e-4)
+    assert torch.allclose(coords.grad.double(), c64.grad, rtol=1e-3, atol=1e-3 * float(c64.grad.abs().max()))
