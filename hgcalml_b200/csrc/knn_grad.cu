@@ -56,6 +56,7 @@ int build_incoming(const int *nidx, int n_vert, int n_neigh, const Incoming &b, 
 // ---- AccumulateKnnGrad: gradient w.r.t. the features ------------------------------------------
 // One warp per target hit m; lanes stride over the features, so the rows of grad_out and of the
 // arg-max table are read coalesced.  Follows modules/compiled/accumulate_knn_grad_kernel.cc:36-99.
+template <int FPL>  // features per lane: lane, lane+32, ..
 __global__ void __launch_bounds__(256)
 acc_grad_features_kernel(const float *__restrict__ grad_out, const float *__restrict__ weights,
                          const int *__restrict__ max_idx, const int *__restrict__ nidx,
@@ -67,9 +68,10 @@ acc_grad_features_kernel(const float *__restrict__ grad_out, const float *__rest
     if (m >= n_vert) return;
     const int e_begin = bounds[m], e_end = bounds[m + 1];
     const float kf = (float)K;
-    for (int f0 = 0; f0 < F; f0 += 32) {
-        const int f = f0 + lane;
-        float acc = 0.f;
+    for (int f0 = 0; f0 < F; f0 += 32 * FPL) {
+        float acc[FPL];
+#pragma unroll
+        for (int u = 0; u < FPL; u++) acc[u] = 0.f;
         for (int p = e_begin; p < e_end; p++) {
             const int e = sedges[p];
             const int i = e / K, k = e - i * K;
@@ -81,16 +83,24 @@ acc_grad_features_kernel(const float *__restrict__ grad_out, const float *__rest
                 for (int kk = lane; kk < k; kk += 32) earlier = earlier || nidx[(size_t)i * K + kk] == i;
                 counts_for_max = !__any_sync(0xffffffffu, earlier);
             }
-            if (f < F) {
-                const float g = grad_out[(size_t)i * G + f];
-                const float mean_part = __fmul_rn(__fdiv_rn(g, kf), w);
-                float max_part = 0.f;
-                if (mean_and_max && counts_for_max && max_idx[(size_t)i * F + f] == m)
-                    max_part = __fmul_rn(grad_out[(size_t)i * G + F + f], w);
-                acc = __fadd_rn(acc, __fadd_rn(mean_part, max_part));
+#pragma unroll
+            for (int u = 0; u < FPL; u++) {
+                const int f = f0 + u * 32 + lane;
+                if (f < F) {
+                    const float g = grad_out[(size_t)i * G + f];
+                    const float mean_part = __fmul_rn(__fdiv_rn(g, kf), w);
+                    float max_part = 0.f;
+                    if (mean_and_max && counts_for_max && max_idx[(size_t)i * F + f] == m)
+                        max_part = __fmul_rn(grad_out[(size_t)i * G + F + f], w);
+                    acc[u] = __fadd_rn(acc[u], __fadd_rn(mean_part, max_part));
+                }
             }
         }
-        if (f < F) grad_feat[(size_t)m * F + f] = acc;
+#pragma unroll
+        for (int u = 0; u < FPL; u++) {
+            const int f = f0 + u * 32 + lane;
+            if (f < F) grad_feat[(size_t)m * F + f] = acc[u];
+        }
     }
 }
 
@@ -101,7 +111,7 @@ __global__ void __launch_bounds__(256)
 acc_grad_weights_kernel(const float *__restrict__ grad_out, const float *__restrict__ feat,
                         const int *__restrict__ max_idx, const int *__restrict__ nidx,
                         float *__restrict__ grad_w, long long n_edges, int n_vert, int K, int F, int G,
-                        bool mean_and_max)
+                        bool mean_and_max, bool vec4)
 {
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= n_edges) return;
@@ -112,10 +122,32 @@ acc_grad_weights_kernel(const float *__restrict__ grad_out, const float *__restr
     const float *x = feat + (size_t)m * F;
     const int *am = max_idx + (size_t)i * F;
     float mean_part = 0.f, max_part = 0.f;
-    for (int f = 0; f < F; f++) {
-        const float xf = __ldg(x + f);
-        mean_part = __fadd_rn(mean_part, __fmul_rn(g[f], xf));
-        if (mean_and_max && am[f] == m) max_part = __fadd_rn(max_part, __fmul_rn(g[F + f], xf));
+    if (vec4) {
+        // rows are 16-byte aligned: four features per load, summed in feature order all the same
+        for (int f = 0; f < F; f += 4) {
+            const float4 xv = __ldg(reinterpret_cast<const float4 *>(x + f));
+            const float4 gv = *reinterpret_cast<const float4 *>(g + f);
+            mean_part = __fadd_rn(mean_part, __fmul_rn(gv.x, xv.x));
+            mean_part = __fadd_rn(mean_part, __fmul_rn(gv.y, xv.y));
+            mean_part = __fadd_rn(mean_part, __fmul_rn(gv.z, xv.z));
+            mean_part = __fadd_rn(mean_part, __fmul_rn(gv.w, xv.w));
+            if (mean_and_max) {
+                const int4 av = *reinterpret_cast<const int4 *>(am + f);
+                if (av.x == m || av.y == m || av.z == m || av.w == m) {
+                    const float4 hv = *reinterpret_cast<const float4 *>(g + F + f);
+                    if (av.x == m) max_part = __fadd_rn(max_part, __fmul_rn(hv.x, xv.x));
+                    if (av.y == m) max_part = __fadd_rn(max_part, __fmul_rn(hv.y, xv.y));
+                    if (av.z == m) max_part = __fadd_rn(max_part, __fmul_rn(hv.z, xv.z));
+                    if (av.w == m) max_part = __fadd_rn(max_part, __fmul_rn(hv.w, xv.w));
+                }
+            }
+        }
+    } else {
+        for (int f = 0; f < F; f++) {
+            const float xf = __ldg(x + f);
+            mean_part = __fadd_rn(mean_part, __fmul_rn(g[f], xf));
+            if (mean_and_max && am[f] == m) max_part = __fadd_rn(max_part, __fmul_rn(g[F + f], xf));
+        }
     }
     // the reference scales by the double 1./(float)K
     mean_part = (float)__dmul_rn((double)mean_part, 1.0 / (double)(float)K);
@@ -206,15 +238,23 @@ extern "C" int hgc_accumulate_knn_grad(
     }
     if (int rc = build_incoming(d_neigh_indices, n_vert, n_neigh, b, stream)) return rc;
     if (n_feat > 0) {
-        acc_grad_features_kernel<<<div_up(n_vert, 8), 256, 0, stream>>>(
-                d_grad_from_out_features, d_distances, d_max_feat_indices, d_neigh_indices, b.bounds, b.sedges,
-                d_out_grad_features, n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0);
+#define HGC_FEAT(FPL)                                                                               \
+    acc_grad_features_kernel<FPL><<<div_up(n_vert, 8), 256, 0, stream>>>(                           \
+            d_grad_from_out_features, d_distances, d_max_feat_indices, d_neigh_indices, b.bounds, b.sedges, \
+            d_out_grad_features, n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0)
+        if (n_feat <= 32) HGC_FEAT(1);
+        else if (n_feat <= 64) HGC_FEAT(2);
+        else HGC_FEAT(4);
+#undef HGC_FEAT
         HGC_LAUNCH_CHECK();
     }
     const long long ne = (long long)n_vert * n_neigh;
+    auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec4 = n_feat % 4 == 0 && aligned16(d_feat) && aligned16(d_grad_from_out_features) &&
+                      (!mean_and_max || aligned16(d_max_feat_indices));
     acc_grad_weights_kernel<<<div_up(ne, 256), 256, 0, stream>>>(
             d_grad_from_out_features, d_feat, d_max_feat_indices, d_neigh_indices, d_out_grad_distances, ne,
-            n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0);
+            n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0, vec4);
     HGC_LAUNCH_CHECK();
     return HGC_OK;
 }

@@ -3,8 +3,9 @@
 // Each pass is a counting sort on one digit:
 //   1. digit_count_kernel   : every block counts the digits of its tile (per-warp counters,
 //                             warp peers found with __match_any_sync, no atomics)
-//   2. scan_hist_kernel     : exclusive scan of the [digit][block] table (digit-major, so a
-//                             digit's blocks are contiguous and block order = input order)
+//   2. scan_*_kernel        : exclusive scan of the [digit][block] table (digit-major, so a
+//                             digit's blocks are contiguous and block order = input order);
+//                             long tables are scanned tile-wise by many blocks
 //   3. digit_scatter_kernel : every block recomputes the rank of each item inside its
 //                             (warp, digit) run and scatters to its final place.
 // A warp owns a contiguous run of its block's tile and walks it 32 items at a time, so equal
@@ -92,6 +93,52 @@ __global__ void __launch_bounds__(1024) scan_hist_kernel(int *__restrict__ data,
     }
 }
 
+// Exclusive scan of a long table in three steps: every block scans its own tile of kScanTile ints
+// and records the tile total, one block scans the totals (scan_hist_kernel), the totals are added back.
+constexpr int kScanTile = 4096;
+
+__global__ void __launch_bounds__(1024) scan_tiles_kernel(int *__restrict__ data, int len, int *__restrict__ tile_sums)
+{
+    __shared__ int warp_sums[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int base = blockIdx.x * kScanTile + threadIdx.x * 4;
+    int v[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) v[q] = base + q < len ? data[base + q] : 0;
+    const int mine = v[0] + v[1] + v[2] + v[3];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int s = warp_sums[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, s, o);
+            if (lane >= o) s += t;
+        }
+        warp_sums[lane] = s;
+    }
+    __syncthreads();
+    int run = (warp == 0 ? 0 : warp_sums[warp - 1]) + incl - mine;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        if (base + q < len) data[base + q] = run;
+        run += v[q];
+    }
+    if (threadIdx.x == 1023) tile_sums[blockIdx.x] = warp_sums[31];
+}
+
+__global__ void add_tile_offsets_kernel(int *__restrict__ data, int len, const int *__restrict__ tile_sums)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < len) data[i] += tile_sums[i / kScanTile];
+}
+
 __global__ void __launch_bounds__(kSortThreads)
 digit_scatter_kernel(const int *__restrict__ keys_in, const int *__restrict__ vals_in,
                      int *__restrict__ keys_out, int *__restrict__ vals_out, int n, int shift,
@@ -168,7 +215,11 @@ __global__ void fill_int_kernel(int *__restrict__ p, int n, int v)
 
 }  // namespace
 
-size_t sort_hist_ints(int n) { return (size_t)kDigits * (size_t)div_up(n > 0 ? n : 1, kTile); }
+size_t sort_hist_ints(int n)
+{
+    const size_t table = (size_t)kDigits * (size_t)div_up(n > 0 ? n : 1, kTile);
+    return table + (table + kScanTile - 1) / kScanTile + 1;  // digit table + its tile totals
+}
 
 int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_out,
                int *keys_tmp, int *vals_tmp, int *block_hist, int n, int key_bits,
@@ -187,8 +238,20 @@ int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_
         const int shift = 8 * p;
         digit_count_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, n, shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();
-        scan_hist_kernel<<<1, 1024, 0, stream>>>(block_hist, kDigits * n_blocks);
-        HGC_LAUNCH_CHECK();
+        const int table = kDigits * n_blocks;
+        if (table <= 4 * kScanTile) {
+            scan_hist_kernel<<<1, 1024, 0, stream>>>(block_hist, table);
+            HGC_LAUNCH_CHECK();
+        } else {
+            const int n_tiles = div_up(table, kScanTile);
+            int *tile_sums = block_hist + table;
+            scan_tiles_kernel<<<n_tiles, 1024, 0, stream>>>(block_hist, table, tile_sums);
+            HGC_LAUNCH_CHECK();
+            scan_hist_kernel<<<1, 1024, 0, stream>>>(tile_sums, n_tiles);
+            HGC_LAUNCH_CHECK();
+            add_tile_offsets_kernel<<<div_up(table, 256), 256, 0, stream>>>(block_hist, table, tile_sums);
+            HGC_LAUNCH_CHECK();
+        }
         digit_scatter_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, src_v, kbuf[dst], vbuf[dst], n,
                                                                     shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();

@@ -173,6 +173,44 @@ private:
     bool mean_and_max_;
 };
 
+// ------------------------------------------------------------------ AccumulateKnnGrad
+class AccumulateKnnGradGpuOp : public OpKernel {
+public:
+    explicit AccumulateKnnGradGpuOp(OpKernelConstruction *c) : OpKernel(c) {}
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &g = ctx->input(0), &w = ctx->input(1), &feat = ctx->input(2), &idx = ctx->input(3),
+                     &maxidx = ctx->input(4);
+        const int n_vert = g.dim_size(0), G = g.dim_size(1), K = idx.dim_size(1), F = feat.dim_size(1);
+        const bool mean_and_max = G > F;  // detected as in accumulate_knn_grad_kernel.cc:246
+        Tensor *gw, *gf;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, K}, &gw));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, F}, &gf));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_knn_grad_workspace_bytes(n_vert, K)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_accumulate_knn_grad(
+            g.flat<float>().data(), w.flat<float>().data(), feat.flat<float>().data(), maxidx.flat<int>().data(),
+            idx.flat<int>().data(), gw->flat<float>().data(), gf->flat<float>().data(), n_vert, K, F, G, 0,
+            mean_and_max, ws.ptr, ws.bytes, StreamOf(ctx)), "AccumulateKnnGrad"));
+    }
+};
+
+// ------------------------------------------------------------------ SelectKnnGrad
+class SelectKnnGradGpuOp : public OpKernel {
+public:
+    explicit SelectKnnGradGpuOp(OpKernelConstruction *c) : OpKernel(c) {}
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &g = ctx->input(0), &idx = ctx->input(1), &dist = ctx->input(2), &coord = ctx->input(3);
+        const int n_vert = coord.dim_size(0), C = coord.dim_size(1), K = dist.dim_size(1);
+        Tensor *out;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, C}, &out));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_knn_grad_workspace_bytes(n_vert, K)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_select_knn_grad(
+            g.flat<float>().data(), idx.flat<int>().data(), dist.flat<float>().data(), coord.flat<float>().data(),
+            out->flat<float>().data(), n_vert, K, C, ws.ptr, ws.bytes, StreamOf(ctx)), "SelectKnnGrad"));
+    }
+};
+
 // ------------------------------------------------------------------ BinnedAssignToCondensates
 // The reference registers a CPU kernel only and its wrapper pins the op to '/cpu'
 // (modules/assign_condensate_op.py:299); this GPU kernel is picked once that pin is removed.
@@ -225,6 +263,13 @@ REGISTER_OP("IndexReplacer").Input("to_be_replaced: int32").Input("replacements:
 REGISTER_OP("AccumulateKnn").Attr("n_moments: int").Attr("mean_and_max: bool")
     .Input("distances: float32").Input("features: float32").Input("indices: int32")
     .Output("out_features: float32").Output("out_max_idxs: int32");
+REGISTER_OP("AccumulateKnnGrad")
+    .Input("grad_from_out_features: float32").Input("distances: float32").Input("features: float32")
+    .Input("neigh_indices: int32").Input("max_feat_indices: int32")
+    .Output("out_grad_distances: float32").Output("out_grad_features: float32");
+REGISTER_OP("SelectKnnGrad")
+    .Input("grad_distances: float32").Input("indices: int32").Input("distances: float32")
+    .Input("coordinates: float32").Output("grad_coords: float32");
 REGISTER_OP("BinnedAssignToCondensates").Attr("beta_threshold: float").Attr("assign_by_max_beta: bool")
     .Input("ccoords: float32").Input("dist: float32").Input("beta: float32").Input("no_condensation_mask: int32")
     .Input("bins_flat: int32").Input("bin_splits: int32").Input("indices_to_filtered: int32")
@@ -239,6 +284,8 @@ REGISTER_KERNEL_BUILDER(Name("BinByCoordinates").Device(DEVICE_GPU).HostMemory("
 REGISTER_KERNEL_BUILDER(Name("BinnedSelectKnn").Device(DEVICE_GPU), BinnedSelectKnnGpuOp);
 REGISTER_KERNEL_BUILDER(Name("IndexReplacer").Device(DEVICE_GPU), IndexReplacerGpuOp);
 REGISTER_KERNEL_BUILDER(Name("AccumulateKnn").Device(DEVICE_GPU), AccumulateKnnGpuOp);
+REGISTER_KERNEL_BUILDER(Name("AccumulateKnnGrad").Device(DEVICE_GPU), AccumulateKnnGradGpuOp);
+REGISTER_KERNEL_BUILDER(Name("SelectKnnGrad").Device(DEVICE_GPU), SelectKnnGradGpuOp);
 REGISTER_KERNEL_BUILDER(Name("BinnedAssignToCondensates").Device(DEVICE_GPU), BinnedAssignToCondensatesGpuOp);
 
 }  // namespace tensorflow
