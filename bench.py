@@ -265,7 +265,7 @@ def main():
     from hgcalml_b200.pipeline import KnnAccumulatePipeline
     del coords, feats
     torch.cuda.empty_cache()
-    pipe = KnnAccumulatePipeline(K, dev, events_per_chunk=max(1, min(8, len(my_events) // 4)), distance_scale=10.)
+    pipe = KnnAccumulatePipeline(K, dev, events_per_chunk=2, distance_scale=10.)
 
     def e2e_step():
         pipe.run(coords_p, feats_p, rs_h, out_p)

@@ -17,7 +17,7 @@ from .binned_select_knn_op import BinnedSelectKnn
 
 
 class KnnAccumulatePipeline:
-    def __init__(self, K: int, device, events_per_chunk: int = 8, distance_scale: float = 10.,
+    def __init__(self, K: int, device, events_per_chunk: int = 2, distance_scale: float = 10.,
                  n_slots: int = 2, with_max_idxs: bool = True):
         self.K = int(K)
         self.device = torch.device(device)
