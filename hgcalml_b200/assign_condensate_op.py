@@ -44,6 +44,41 @@ def _BinnedAssignToCondensates(ccoords, dist, beta, no_condensation_mask, bins_f
     return assigned_h, assigned, alpha, asso, ncond
 
 
+def merge_noise_as_indiv_cp(assignment, asso_idx, alpha_idx, is_cond, n_condensates, row_splits):
+    """modules/assign_condensate_op.py:16-44: every noise hit (assignment < 0) becomes a condensation
+    point of its own.  Per event the noise hits take the shower numbers 0..n_noise-1 in hit order and
+    the real showers are shifted up by n_noise; ``alpha_idx`` lists, per event, the noise hits first
+    and then the condensates; noise hits are associated to themselves and flagged as condensates."""
+    dev = assignment.device
+    rs = row_splits.to(torch.int64)
+    n = assignment.shape[0]
+    num_rows = rs.shape[0] - 1
+    a = assignment[:, 0].to(torch.int64)
+    seg = torch.repeat_interleave(torch.arange(num_rows, device=dev), rs[1:] - rs[:-1])
+    noise = a < 0
+    csum = torch.cumsum(noise.to(torch.int64), 0)
+    before_event = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev), csum])[rs[:-1]]
+    x = torch.where(noise, csum - before_event[seg], torch.zeros_like(csum))  # 1-based rank among the event's noise
+    n_noise = torch.zeros(num_rows, dtype=torch.int64, device=dev).scatter_reduce(0, seg, x, "amax", include_self=True)
+    new_assignment = torch.where(noise, x - 1, a + n_noise[seg]).to(torch.int32)
+
+    allrange = torch.arange(n, device=dev)
+    nc = n_condensates.to(torch.int64)
+    cond_event = torch.repeat_interleave(torch.arange(num_rows, device=dev), nc[1:] - nc[:-1])
+    noise_idx = allrange[noise]
+    # per event: noise hits, then condensates -- a stable sort by (event, kind)
+    keys = torch.cat([seg[noise] * 2, cond_event * 2 + 1])
+    vals = torch.cat([noise_idx, alpha_idx.to(torch.int64)])
+    new_alpha = vals[torch.sort(keys, stable=True).indices].to(torch.int32)
+
+    cond = is_cond[:, 0].clone()
+    cond[asso_idx < 0] = True
+    new_asso = torch.where(asso_idx < 0, allrange.to(asso_idx.dtype), asso_idx)
+    per_event = torch.zeros(num_rows, dtype=torch.int64, device=dev).scatter_add(0, seg, cond.to(torch.int64))
+    new_ncond = torch.cat([n_condensates[0:1].to(torch.int64), torch.cumsum(per_event, 0)]).to(torch.int32)
+    return new_assignment[:, None], new_asso, new_alpha, cond[:, None], new_ncond
+
+
 def _segment_ids_to_row_splits(ids, num_segments):
     counts = torch.bincount(ids.to(torch.int64), minlength=num_segments)
     return torch.cat([torch.zeros(1, dtype=torch.int64, device=ids.device), counts.cumsum(0)]).to(torch.int32)
@@ -56,13 +91,11 @@ def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_thres
 
     Returns ``assignment [N,1], association [N], alpha_idx, is_cond [N,1], n_condensates`` with the
     reference's meaning.  The tensor glue around the op (binning, stable sort by bin, high-beta
-    filter, mapping back) follows the reference line by line on CUDA tensors; the op itself is the
-    library's parallel claim pass."""
+    filter, mapping back, and the ``keep_noise`` renumbering) follows the reference line by line on
+    CUDA tensors; the op itself is the library's parallel claim pass."""
     assert 1 <= nbin_dims <= 6
     assert 0. <= beta_threshold <= 1.
     assert distance_threshold > 0.
-    if keep_noise:
-        raise NotImplementedError("keep_noise=True post-processing is not part of this library")
     ccoords = C.f32(ccoords)
     C.require_cuda(ccoords)
     dev = ccoords.device
@@ -113,4 +146,7 @@ def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_thres
     alpha_idx = alpha[alpha != -1]
     is_cond = torch.zeros((n,), dtype=torch.bool, device=dev)
     is_cond[alpha_idx.to(torch.int64)] = True
-    return assignment[:, None], asso, alpha_idx, is_cond[:, None], n_condensates
+    out = (assignment[:, None], asso, alpha_idx, is_cond[:, None], n_condensates)
+    if keep_noise:
+        out = merge_noise_as_indiv_cp(*out, row_splits)
+    return out

@@ -322,11 +322,33 @@ def _segment_ids_to_row_splits(ids, num_segments):
     return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
 
 
+def merge_noise_as_indiv_cp(assignment, asso_idx, alpha_idx, is_cond, n_condensates, row_splits):
+    """modules/assign_condensate_op.py:16-44, event by event in plain numpy."""
+    assignment = np.array(assignment[:, 0], np.int64)
+    asso_idx = np.array(asso_idx)
+    is_cond = np.array(is_cond[:, 0], bool)
+    new_alpha, new_ncond = [], [int(n_condensates[0])]
+    for e in range(len(row_splits) - 1):
+        lo, hi = int(row_splits[e]), int(row_splits[e + 1])
+        a = assignment[lo:hi]
+        noise = a < 0
+        n_noise = int(noise.sum())
+        a = np.where(noise, np.cumsum(noise) - 1, a + n_noise)
+        assignment[lo:hi] = a
+        new_alpha += list(np.nonzero(noise)[0] + lo) + list(alpha_idx[n_condensates[e]:n_condensates[e + 1]])
+        is_cond[lo:hi] |= asso_idx[lo:hi] < 0
+        new_ncond.append(new_ncond[-1] + int(is_cond[lo:hi].sum()))
+    allrange = np.arange(len(asso_idx))
+    asso_idx = np.where(asso_idx < 0, allrange, asso_idx).astype(asso_idx.dtype)
+    return (assignment.astype(np.int32)[:, None], asso_idx, np.array(new_alpha, np.int32), is_cond[:, None],
+            np.array(new_ncond, np.int32))
+
+
 def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_threshold,
                                     no_condensation_mask=None, distance_threshold=1.,
                                     assign_by_max_beta=False, nbin_dims=3, backend="port",
-                                    return_op_io=False):
-    """modules/assign_condensate_op.py:210-333 without the keep_noise post-processing.
+                                    return_op_io=False, keep_noise=False):
+    """modules/assign_condensate_op.py:210-333.
     Returns (assignment[N,1], association[N], alpha_idx, is_cond[N,1], n_condensates)."""
     ccoords = _c32f(ccoords)
     betas = _c32f(betas).reshape(-1, 1)
@@ -376,6 +398,8 @@ def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_thres
     is_cond = np.zeros((n,), bool)
     is_cond[alpha_idx] = True
     out = (assignment[:, None], asso, alpha_idx, is_cond[:, None], ncond)
+    if keep_noise:
+        out = merge_noise_as_indiv_cp(*out, row_splits)
     if return_op_io:
         return out, op_in, (assigned_h, assignment_s, alpha, asso_s, ncond)
     return out

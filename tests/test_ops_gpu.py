@@ -405,3 +405,15 @@ def test_autograd_through_the_neighbour_path(cuda):
     assert torch.allclose(out.double(), out_ref, rtol=1e-4, atol=1e-5)
     assert torch.allclose(feats.grad.double(), f64.grad, rtol=1e-3, atol=1e-4)
     assert torch.allclose(coords.grad.double(), c64.grad, rtol=1e-3, atol=1e-3 * float(c64.grad.abs().max()))
+
+
+def test_condensates_keep_noise(cuda, oracle):
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    g = load_golden("cond_var_mindist")
+    for amb in (True, False):
+        ref = oracle.BuildAndAssignCondensatesBinned(g["ccoords"], g["betas"], g["dist"], g["row_splits"], 0.1,
+                                                     assign_by_max_beta=amb, keep_noise=True)
+        got = BuildAndAssignCondensatesBinned(T(g["ccoords"], cuda), T(g["betas"], cuda), T(g["dist"], cuda),
+                                              T(g["row_splits"], cuda), 0.1, assign_by_max_beta=amb, keep_noise=True)
+        for r, gt, key in zip(ref, got, COND_KEYS):
+            assert np.array_equal(N(gt), r), key

@@ -161,3 +161,22 @@ def test_select_knn_grad_restatement_is_the_gradient(oracle):
         np.add.at(ref, np.nonzero(ok)[0], contrib)
         np.add.at(ref, m[ok], -contrib)
     assert np.allclose(got, ref, rtol=1e-4, atol=1e-4 * np.abs(ref).max())
+
+
+def test_keep_noise_invariants(oracle):
+    """keep_noise=True (modules/assign_condensate_op.py:16-44): afterwards no hit is noise, showers are
+    numbered 0..n-1 per event with alpha_idx as their representatives -- the round trips the
+    reference's unit test asserts (tests/unit/condensate.py:88-112)."""
+    g = load_golden("cond_var_maxbeta")
+    out = oracle.BuildAndAssignCondensatesBinned(g["ccoords"], g["betas"], g["dist"], g["row_splits"], 0.1,
+                                                 assign_by_max_beta=True, keep_noise=True)
+    assignment, asso, alpha, is_cond, ncond = out
+    rs = g["row_splits"]
+    assert (assignment >= 0).all() and (asso >= 0).all()
+    assert is_cond.sum() == len(alpha) == ncond[-1]
+    for e in range(len(rs) - 1):
+        al = alpha[ncond[e]:ncond[e + 1]]
+        assert np.array_equal(assignment[al, 0], np.arange(len(al)))
+        assert np.array_equal(asso[al], al)
+        a = assignment[rs[e]:rs[e + 1], 0]
+        assert a.max() + 1 == len(al)
