@@ -39,6 +39,9 @@ typedef double knn_key;
 #else
 #define HGC_STAT(x)
 #endif
+#ifndef HGC_KNN_FLUSH_AT
+#define HGC_KNN_FLUSH_AT 32
+#endif
 #ifndef HGC_KNN_MIN_BLOCKS
 #define HGC_KNN_MIN_BLOCKS 4
 #endif
@@ -129,17 +132,35 @@ __device__ __forceinline__ Point<NV4> load_point(const float4 *__restrict__ pts,
 
 // sum over coordinates of (a-b)^2, each operation rounded on its own, in coordinate order.  The
 // zero padding of the last float4 adds +0 terms, which change nothing.
+// Packed float32x2 subtract / multiply (two individually rounded float32 operations per instruction).
+__device__ __forceinline__ float2 sub2(float ax, float ay, float bx, float by)
+{
+    float2 r;
+    asm("{ .reg .b64 ra, rb, rr; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; sub.rn.f32x2 rr, ra, rb; "
+        "mov.b64 {%0,%1}, rr; }"
+        : "=f"(r.x), "=f"(r.y) : "f"(ax), "f"(ay), "f"(bx), "f"(by));
+    return r;
+}
+__device__ __forceinline__ float2 sqr2(float2 a)
+{
+    float2 r;
+    asm("{ .reg .b64 ra, rr; mov.b64 ra, {%2,%3}; mul.rn.f32x2 rr, ra, ra; mov.b64 {%0,%1}, rr; }"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y));
+    return r;
+}
+
 template <int NV4>
 __device__ __forceinline__ float distsq(const Point<NV4> &a, const Point<NV4> &b)
 {
     float s = 0.f;
 #pragma unroll
     for (int u = 0; u < NV4; u++) {
-        float t;
-        t = __fsub_rn(a.v[u].x, b.v[u].x); s = __fadd_rn(s, __fmul_rn(t, t));
-        t = __fsub_rn(a.v[u].y, b.v[u].y); s = __fadd_rn(s, __fmul_rn(t, t));
-        t = __fsub_rn(a.v[u].z, b.v[u].z); s = __fadd_rn(s, __fmul_rn(t, t));
-        t = __fsub_rn(a.v[u].w, b.v[u].w); s = __fadd_rn(s, __fmul_rn(t, t));
+        const float2 q01 = sqr2(sub2(a.v[u].x, a.v[u].y, b.v[u].x, b.v[u].y));
+        const float2 q23 = sqr2(sub2(a.v[u].z, a.v[u].w, b.v[u].z, b.v[u].w));
+        s = __fadd_rn(s, q01.x);
+        s = __fadd_rn(s, q01.y);
+        s = __fadd_rn(s, q23.x);
+        s = __fadd_rn(s, q23.y);
     }
     return s;
 }
@@ -234,7 +255,7 @@ struct Query {
         if (pass) buf[buffered + __popc(m & ((1u << lane) - 1u))] = key;
         buffered += __popc(m);
         HGC_STAT(n_accepted += __popc(m));
-        if (buffered >= kWarp) flush();
+        if (buffered >= HGC_KNN_FLUSH_AT) flush();
     }
 };
 
