@@ -78,6 +78,22 @@ __device__ __forceinline__ knn_key warp_sort(knn_key v, int lane)
     return v;
 }
 
+// Ascending sort of one 32-bit word per lane (same network).
+__device__ __forceinline__ unsigned warp_sort_u32(unsigned v, int lane)
+{
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+        unsigned o = __shfl_xor_sync(0xffffffffu, v, k - 1);
+        v = ((lane & (k >> 1)) == 0) ? min(v, o) : max(v, o);
+#pragma unroll
+        for (int j = k >> 2; j > 0; j >>= 1) {
+            o = __shfl_xor_sync(0xffffffffu, v, j);
+            v = ((lane & j) == 0) ? min(v, o) : max(v, o);
+        }
+    }
+    return v;
+}
+
 // Sorts a bitonic sequence (one key per lane) ascending.
 __device__ __forceinline__ knn_key warp_bitonic_merge(knn_key v, int lane)
 {
@@ -411,24 +427,26 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
                             HGC_STAT(const long long tb0 = clock64());
                             const int v = v0 + lane;
                             int chunk = 0, r_begin = 0, r_end = 0;
-                            knn_key order_key = HGC_KNN_INF_KEY;
+                            // order word: box distance with its 5 lowest mantissa bits replaced by the lane
+                            // (rounding a non-negative float down keeps it a lower bound)
+                            unsigned order_key = 0xffffffffu;
                             if (v < total_chunks) {
                                 while (v >= s_end[warp][r]) r++;
                                 chunk = s_start[warp][r] + v;
                                 r_begin = s_rbeg[warp][r];
                                 r_end = s_rend[warp][r];
                                 const float lb = box_distsq<NV4>(Q.q, a.chunk_lo, a.chunk_hi, (size_t)chunk);
-                                if (lb <= Q.kth()) order_key = make_key(lb, lane);
+                                if (lb <= Q.kth()) order_key = (__float_as_uint(lb) & ~31u) | (unsigned)lane;
                             }
                             HGC_STAT(st_boxes += min(total_chunks - v0, kWarp));
-                            const int alive = __popc(__ballot_sync(0xffffffffu, order_key != HGC_KNN_INF_KEY));
+                            const int alive = __popc(__ballot_sync(0xffffffffu, order_key != 0xffffffffu));
                             if (alive == 0) continue;
-                            order_key = warp_sort(order_key, lane);
+                            order_key = warp_sort_u32(order_key, lane);
                             HGC_STAT(t_box += clock64() - tb0);
                             for (int n = 0; n < alive; n++) {
-                                const knn_key ok = shfl_key(order_key, n);
-                                if (key_distsq(ok) > Q.kth()) break;  // sorted: the remaining boxes are farther still
-                                const int src = key_index(ok);
+                                const unsigned ok = __shfl_sync(0xffffffffu, order_key, n);
+                                if (__uint_as_float(ok & ~31u) > Q.kth()) break;  // sorted: the remaining boxes are farther still
+                                const int src = (int)(ok & 31u);
                                 const int c = __shfl_sync(0xffffffffu, chunk, src);
                                 const int rb = __shfl_sync(0xffffffffu, r_begin, src);
                                 const int re = __shfl_sync(0xffffffffu, r_end, src);
