@@ -417,3 +417,54 @@ def test_condensates_keep_noise(cuda, oracle):
                                               T(g["row_splits"], cuda), 0.1, assign_by_max_beta=amb, keep_noise=True)
         for r, gt, key in zip(ref, got, COND_KEYS):
             assert np.array_equal(N(gt), r), key
+
+
+# ------------------------------------------------------------------ error reporting
+def test_status_word_and_argument_errors(cuda, oracle):
+    """Device-side anomalies set the workspace status word instead of printing; host-side problems
+    come back as error codes."""
+    from hgcalml_b200 import _capi as C
+    coords = np.array([[0.1, 0.2], [5.0, 0.3], [0.4, 0.1]], np.float32)  # 5.0 lies outside 3 bins of width 1
+    rs = np.array([0, 3], np.int32)
+    t = dict(c=T(coords, cuda), rs=T(rs, cuda), bw=T(np.array([1.0], np.float32), cuda),
+             nb=T(np.array([3, 3], np.int32), cuda))
+    assigned = torch.zeros((3, 3), dtype=torch.int32, device=cuda)
+    flat = torch.zeros((3,), dtype=torch.int32, device=cuda)
+    nper = torch.zeros((9,), dtype=torch.int32, device=cuda)
+    need = C.lib.hgc_bin_by_coordinates_workspace_bytes(3, 2, 2, 9)
+    ws = C.workspace(need, cuda)
+    args = (C.ptr(t["c"]), C.ptr(t["rs"]), C.ptr(t["bw"]), C.ptr(t["nb"]), C.ptr(assigned), C.ptr(flat), C.ptr(nper),
+            3, 2, 2, 9, 1)
+    assert C.lib.hgc_bin_by_coordinates(*args, C.ptr(ws), ws.numel(), C.stream_of(ws)) == 0
+    assert C.read_status(ws, raise_on_flag=False) == 1  # HGC_STATUS_BIN_OUT_OF_RANGE
+    with pytest.raises(C.HgcError):
+        C.read_status(ws)
+    # same result as the reference, which forces the index to 0 (bin_by_coordinates_kernel.cc:75-78)
+    ref = oracle.op_bin_by_coordinates(coords, rs, np.array([1.0], np.float32), np.array([3, 3], np.int32))
+    assert np.array_equal(N(assigned), ref[0]) and np.array_equal(N(flat), ref[1]) and np.array_equal(N(nper), ref[2])
+    # workspace too small / misaligned
+    assert C.lib.hgc_bin_by_coordinates(*args, C.ptr(ws), 16, C.stream_of(ws)) == -2
+    off = ws[8:]
+    assert C.lib.hgc_bin_by_coordinates(*args, C.ptr(off), off.numel(), C.stream_of(ws)) == -2
+    # a clean call leaves the status word at zero
+    coords_ok = np.array([[0.1, 0.2], [2.0, 0.3], [0.4, 0.1]], np.float32)
+    args_ok = (C.ptr(T(coords_ok, cuda)),) + args[1:]
+    assert C.lib.hgc_bin_by_coordinates(*args_ok, C.ptr(ws), ws.numel(), C.stream_of(ws)) == 0
+    assert C.read_status(ws) == 0
+
+
+def test_python_mirror_repeats_the_ops_argument_checks(cuda):
+    from hgcalml_b200 import _capi as C
+    from hgcalml_b200.accknn_op import AccumulateLinKnn
+    from hgcalml_b200.binned_select_knn_op import _BinnedSelectKnn
+    z = lambda *s, dt=torch.float32: torch.zeros(s, dtype=dt, device=cuda)  # noqa: E731
+    with pytest.raises(C.HgcError, match="second dimension"):
+        AccumulateLinKnn(z(4, 3), z(4, 8), z(4, 2, dt=torch.int32))
+    with pytest.raises(C.HgcError, match="first dimensions"):
+        AccumulateLinKnn(z(4, 2), z(5, 8), z(4, 2, dt=torch.int32))
+    with pytest.raises(C.HgcError, match="at least 2 binning"):
+        _BinnedSelectKnn(4, z(4, 3), z(4, dt=torch.int32), z(4, 2, dt=torch.int32), z(5, dt=torch.int32),
+                         z(1, dt=torch.int32), z(1))
+    with pytest.raises(C.HgcError, match="singleton"):
+        _BinnedSelectKnn(4, z(4, 3), z(4, dt=torch.int32), z(4, 3, dt=torch.int32), z(5, dt=torch.int32),
+                         z(2, dt=torch.int32), z(2))
