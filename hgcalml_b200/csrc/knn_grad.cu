@@ -9,6 +9,7 @@
 // order -- no atomics, run-to-run identical, and for AccumulateKnnGrad the same order as the
 // reference's CPU loop, so the result is bit-identical to it.
 #include "common.cuh"
+#include "incoming.cuh"
 
 namespace hgc {
 namespace {
@@ -20,37 +21,6 @@ __global__ void edge_target_keys_kernel(const int *__restrict__ nidx, long long 
     if (e >= n_edges) return;
     const int m = nidx[e];
     keys[e] = (m >= 0 && m < n_vert) ? m : n_vert;  // sentinel: sorts last, belongs to no hit
-}
-
-struct Incoming {
-    int *keys, *skeys, *sedges, *tkeys, *tvals, *hist, *bounds;
-};
-
-template <typename W>
-Incoming incoming_layout(W &ws, int n_vert, int n_neigh)
-{
-    const size_t ne = (size_t)(n_vert > 0 ? n_vert : 0) * (size_t)(n_neigh > 0 ? n_neigh : 0);
-    Incoming b;
-    b.keys = ws.template take<int>(ne);
-    b.skeys = ws.template take<int>(ne);
-    b.sedges = ws.template take<int>(ne);
-    b.tkeys = ws.template take<int>(ne);
-    b.tvals = ws.template take<int>(ne);
-    b.hist = ws.template take<int>(sort_hist_ints((int)ne));
-    b.bounds = ws.template take<int>((size_t)(n_vert > 0 ? n_vert : 0) + 2);
-    return b;
-}
-
-// bounds[m] .. bounds[m+1]: positions in sedges of the edges whose neighbour is m
-int build_incoming(const int *nidx, int n_vert, int n_neigh, const Incoming &b, cudaStream_t stream)
-{
-    const long long ne = (long long)n_vert * n_neigh;
-    edge_target_keys_kernel<<<div_up(ne, 256), 256, 0, stream>>>(nidx, ne, n_vert, b.keys);
-    HGC_LAUNCH_CHECK();
-    if (int rc = sort_pairs(b.keys, nullptr, b.skeys, b.sedges, b.tkeys, b.tvals, b.hist, (int)ne,
-                            bits_for(n_vert), stream))
-        return rc;
-    return boundaries_from_sorted_keys(b.skeys, (int)ne, b.bounds, n_vert, stream);
 }
 
 // ---- AccumulateKnnGrad: gradient w.r.t. the features ------------------------------------------
@@ -186,19 +156,26 @@ select_grad_kernel(const float *__restrict__ grad_dist, const int *__restrict__ 
     grad_coord[t] = val;
 }
 
-struct SizerW {
-    Sizer s;
-    template <typename T> T *take(size_t n) { s.take<T>(n); return nullptr; }
-};
-
 }  // namespace
+
+int build_incoming(const int *nidx, int n_vert, int n_neigh, const Incoming &b, cudaStream_t stream)
+{
+    const long long ne = (long long)n_vert * n_neigh;
+    edge_target_keys_kernel<<<div_up(ne, 256), 256, 0, stream>>>(nidx, ne, n_vert, b.keys);
+    HGC_LAUNCH_CHECK();
+    if (int rc = sort_pairs(b.keys, nullptr, b.skeys, b.sedges, b.tkeys, b.tvals, b.hist, (int)ne,
+                            bits_for(n_vert), stream))
+        return rc;
+    return boundaries_from_sorted_keys(b.skeys, (int)ne, b.bounds, n_vert, stream);
+}
+
 }  // namespace hgc
 
 using namespace hgc;
 
 extern "C" size_t hgc_knn_grad_workspace_bytes(int n_vert, int n_neigh)
 {
-    SizerW w;
+    IncomingSizer w;
     incoming_layout(w, n_vert, n_neigh);
     return w.s.used;
 }

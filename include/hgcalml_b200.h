@@ -233,6 +233,25 @@ int hgc_select_knn_grad(
         float *d_grad_coord, int n_vert, int n_neigh, int n_coords,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Sibling ops on the same neighbour tables (used by the graph-condensation layers).
+ *
+ * LocalDistance -- replaces LocalDistanceOpFunctor (modules/compiled/local_distance_kernel.h):
+ * d_distances[i,k] = squared distance between hit i and hit d_neigh_idxs[i,k]; 0 for -1 and for the
+ * hit itself.  d_coords [n_in_vert, n_coords], d_neigh_idxs / d_distances [n_out_vert, n_neigh].
+ *
+ * PushKnn -- replaces PushKnnOpFunctor (modules/compiled/push_knn_kernel.h):
+ * d_out_feat[m,f] = sum over all (i,k) with d_idxs[i,k] == m of d_feat[i,f] * d_weights[i,k], summed
+ * in (i,k) order without atomics (bit-identical to the reference's CPU loop).  Workspace:
+ * hgc_knn_grad_workspace_bytes(n_vert, n_neigh).
+ * ------------------------------------------------------------------------------------- */
+int hgc_local_distance(
+        const int *d_neigh_idxs, const float *d_coords, float *d_distances,
+        int n_coords, int n_in_vert, int n_out_vert, int n_neigh, hgc_stream_t stream);
+int hgc_push_knn(
+        const float *d_weights, const float *d_feat, const int *d_idxs, float *d_out_feat,
+        int n_vert, int n_neigh, int n_feat, void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

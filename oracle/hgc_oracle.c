@@ -442,3 +442,42 @@ void oracle_select_knn_grad(
             }
         }
 }
+
+/* ------------------------------------------------------------------------
+ * LocalDistance
+ * restates modules/compiled/local_distance_kernel.cc:22-70: squared distance from
+ * every hit to each of its listed neighbours (0 for padding and for the hit itself).
+ * ---------------------------------------------------------------------- */
+void oracle_local_distance(const int *nidx, const float *coords, float *dist,
+                           int n_coords, int n_in_vert, int n_out_vert, int n_neigh)
+{
+    (void)n_in_vert;
+    for (int i = 0; i < n_out_vert; i++)
+        for (int k = 0; k < n_neigh; k++) {
+            const int j = nidx[(size_t)i * n_neigh + k];
+            float d = 0.f;
+            if (j >= 0 && j != i)
+                d = oracle_distsq(coords + (size_t)i * n_coords, coords + (size_t)j * n_coords, n_coords);
+            dist[(size_t)i * n_neigh + k] = d;
+        }
+}
+
+/* ------------------------------------------------------------------------
+ * PushKnn
+ * restates modules/compiled/push_knn_kernel.cc:35-71: every hit adds its weighted
+ * features to each of its neighbours, out[m,f] += feat[i,f] * w[i,k], in (i, k) order.
+ * ---------------------------------------------------------------------- */
+void oracle_push_knn(const float *weights, const float *feat, const int *nidx, float *out,
+                     int n_vert, int n_neigh, int n_feat)
+{
+    for (size_t t = 0; t < (size_t)n_vert * n_feat; t++) out[t] = 0.f;
+    for (int i = 0; i < n_vert; i++)
+        for (int f = 0; f < n_feat; f++) {
+            const float x = feat[(size_t)i * n_feat + f];
+            for (int k = 0; k < n_neigh; k++) {
+                const int m = nidx[(size_t)i * n_neigh + k];
+                if (m < 0) continue;
+                out[(size_t)m * n_feat + f] += x * weights[(size_t)i * n_neigh + k];
+            }
+        }
+}

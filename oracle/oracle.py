@@ -195,6 +195,27 @@ def op_select_knn_grad(grad_dist, indices, coords):
     return out
 
 
+def op_local_distance(coords, neigh_idxs, backend="port"):
+    """Functor of local_distance_kernel.cc:47-70. Returns distsq [n_out_vert, K]."""
+    coords = _c32f(coords)
+    nidx = _c32i(neigh_idxs)
+    out = np.zeros(nidx.shape, np.float32)
+    lib(backend).fn("local_distance")(_i(nidx), _f(coords), _f(out), c_int(coords.shape[1]),
+                                      c_int(coords.shape[0]), c_int(nidx.shape[0]), c_int(nidx.shape[1]))
+    return out
+
+
+def op_push_knn(weights, features, indices, backend="port"):
+    """Functor of push_knn_kernel.cc:35-71. Returns out_features [N, F]."""
+    weights = _c32f(weights)
+    features = _c32f(features)
+    indices = _c32i(indices)
+    out = np.zeros_like(features)
+    lib(backend).fn("push_knn")(_f(weights), _f(features), _i(indices), _f(out), c_int(features.shape[0]),
+                                c_int(indices.shape[1]), c_int(features.shape[1]))
+    return out
+
+
 def op_binned_assign_to_condensates(ccoords, dist, beta, mask, bins_flat, bin_splits,
                                     indices_to_filtered, original_indices_h, row_splits, n_bins,
                                     bin_width, ccoords_h, dist_h, beta_h, mask_h, row_splits_h,

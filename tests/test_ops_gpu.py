@@ -468,3 +468,24 @@ def test_python_mirror_repeats_the_ops_argument_checks(cuda):
     with pytest.raises(C.HgcError, match="singleton"):
         _BinnedSelectKnn(4, z(4, 3), z(4, dt=torch.int32), z(4, 3, dt=torch.int32), z(5, dt=torch.int32),
                          z(2, dt=torch.int32), z(2))
+
+
+# ------------------------------------------------------------------ sibling ops
+def test_local_distance_and_push_knn_vs_checker(cuda, oracle):
+    from hgcalml_b200.local_distance_op import LocalDistance
+    from hgcalml_b200.push_knn_op import PushKnn
+    rng = np.random.default_rng(21)
+    n, K, F, Cd = 6000, 20, 24, 5
+    idx = rng.integers(-1, n, (n, K)).astype(np.int32)
+    idx[:, 0] = np.arange(n)
+    c = rng.standard_normal((n, Cd)).astype(np.float32)
+    w = rng.random((n, K), dtype=np.float32)
+    f = rng.standard_normal((n, F), dtype=np.float32)
+    d = LocalDistance(T(c, cuda), T(idx, cuda))
+    assert np.array_equal(bits(N(d)), bits(oracle.op_local_distance(c, idx)))
+    out = PushKnn(T(w, cuda), T(f, cuda), T(idx, cuda))
+    assert np.array_equal(bits(N(out)), bits(oracle.op_push_knn(w, f, idx)))
+    # LocalDistance reproduces the distances the search reports for its own neighbour lists
+    g = load_golden("knn_showers4d")
+    d2 = LocalDistance(T(g["coords"], cuda), T(g["idx"], cuda))
+    assert np.array_equal(bits(N(d2)), bits(g["dist"]))
