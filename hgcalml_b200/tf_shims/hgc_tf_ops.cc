@@ -3,7 +3,7 @@
 //
 // Each shim keeps the reference's op name, attributes, input/output order and dtypes
 // (modules/compiled/{bin_by_coordinates,binned_select_knn,index_replacer,accumulate_knn,
-// binned_assign_to_condensates}_module.cc), so the unchanged Python wrappers load it with
+// accumulate_knn_grad,select_knn_grad,local_distance,push_knn,binned_assign_to_condensates}_module.cc), so the unchanged Python wrappers load it with
 // tf.load_op_library.  A shim does shape checks, allocate_output / allocate_temp, and ONE call
 // into the library on the op's own CUDA stream; it never synchronises the device.
 //
@@ -211,6 +211,37 @@ public:
     }
 };
 
+// ------------------------------------------------------------------ LocalDistance, PushKnn
+class LocalDistanceGpuOp : public OpKernel {
+public:
+    explicit LocalDistanceGpuOp(OpKernelConstruction *c) : OpKernel(c) {}
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &coords = ctx->input(0), &idx = ctx->input(1);
+        const int n_in = coords.dim_size(0), C = coords.dim_size(1), n_out = idx.dim_size(0), K = idx.dim_size(1);
+        Tensor *dist;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_out, K}, &dist));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_local_distance(idx.flat<int>().data(), coords.flat<float>().data(),
+                                                       dist->flat<float>().data(), C, n_in, n_out, K, StreamOf(ctx)),
+                                    "LocalDistance"));
+    }
+};
+
+class PushKnnGpuOp : public OpKernel {
+public:
+    explicit PushKnnGpuOp(OpKernelConstruction *c) : OpKernel(c) {}
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &w = ctx->input(0), &feat = ctx->input(1), &idx = ctx->input(2);
+        const int n_vert = feat.dim_size(0), F = feat.dim_size(1), K = idx.dim_size(1);
+        Tensor *out;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, F}, &out));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_knn_grad_workspace_bytes(n_vert, K)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_push_knn(w.flat<float>().data(), feat.flat<float>().data(),
+                                                 idx.flat<int>().data(), out->flat<float>().data(), n_vert, K, F,
+                                                 ws.ptr, ws.bytes, StreamOf(ctx)), "PushKnn"));
+    }
+};
+
 // ------------------------------------------------------------------ BinnedAssignToCondensates
 // The reference registers a CPU kernel only and its wrapper pins the op to '/cpu'
 // (modules/assign_condensate_op.py:299); this GPU kernel is picked once that pin is removed.
@@ -270,6 +301,9 @@ REGISTER_OP("AccumulateKnnGrad")
 REGISTER_OP("SelectKnnGrad")
     .Input("grad_distances: float32").Input("indices: int32").Input("distances: float32")
     .Input("coordinates: float32").Output("grad_coords: float32");
+REGISTER_OP("LocalDistance").Input("coordinates: float32").Input("neighbour_idxs: int32").Output("distances: float32");
+REGISTER_OP("PushKnn").Input("weights: float32").Input("features: float32").Input("indices: int32")
+    .Output("out_features: float32");
 REGISTER_OP("BinnedAssignToCondensates").Attr("beta_threshold: float").Attr("assign_by_max_beta: bool")
     .Input("ccoords: float32").Input("dist: float32").Input("beta: float32").Input("no_condensation_mask: int32")
     .Input("bins_flat: int32").Input("bin_splits: int32").Input("indices_to_filtered: int32")
@@ -286,6 +320,8 @@ REGISTER_KERNEL_BUILDER(Name("IndexReplacer").Device(DEVICE_GPU), IndexReplacerG
 REGISTER_KERNEL_BUILDER(Name("AccumulateKnn").Device(DEVICE_GPU), AccumulateKnnGpuOp);
 REGISTER_KERNEL_BUILDER(Name("AccumulateKnnGrad").Device(DEVICE_GPU), AccumulateKnnGradGpuOp);
 REGISTER_KERNEL_BUILDER(Name("SelectKnnGrad").Device(DEVICE_GPU), SelectKnnGradGpuOp);
+REGISTER_KERNEL_BUILDER(Name("LocalDistance").Device(DEVICE_GPU), LocalDistanceGpuOp);
+REGISTER_KERNEL_BUILDER(Name("PushKnn").Device(DEVICE_GPU), PushKnnGpuOp);
 REGISTER_KERNEL_BUILDER(Name("BinnedAssignToCondensates").Device(DEVICE_GPU), BinnedAssignToCondensatesGpuOp);
 
 }  // namespace tensorflow
