@@ -76,3 +76,19 @@ def test_product_does_not_import_checker():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cc")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src, os.path.join(dirpath, f)
+
+
+def test_tf_shims_type_check_against_api_stub():
+    """TensorFlow is not installed where this suite runs; the shims are at least parsed and
+    type-checked against declarations of the custom-op API they use and against the C header."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    cuda_inc = "/usr/local/cuda/include"
+    if gxx is None or not os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")):
+        pytest.skip("needs g++ and the CUDA headers")
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-I" + os.path.join(ROOT, "tests", "tf_api_stub"),
+                        "-I" + os.path.join(ROOT, "include"), "-I" + cuda_inc,
+                        os.path.join(ROOT, "hgcalml_b200", "tf_shims", "hgc_tf_ops.cc")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
