@@ -48,6 +48,7 @@ def _load():
         "hgc_binned_select_knn_ragged": (I, [P] * 6 + [I] * 8 + [P, S, P]),
         "hgc_local_distance": (I, [P, P, P, I, I, I, I, P]),
         "hgc_push_knn": (I, [P, P, P, P, I, I, I, P, S, P]),
+        "hgc_push_knn_grad": (I, [P] * 6 + [I] * 3 + [P]),
         "hgc_knn_grad_workspace_bytes": (S, [I, I]),
         "hgc_accumulate_knn_grad": (I, [P] * 7 + [I] * 6 + [P, S, P]),
         "hgc_select_knn_grad": (I, [P] * 5 + [I] * 3 + [P, S, P]),

@@ -48,10 +48,71 @@ push_knn_kernel(const float *__restrict__ weights, const float *__restrict__ fea
     }
 }
 
+// PushKnnGrad (modules/compiled/push_knn_grad_kernel.cc:22-95): both parts are gathers.
+// feat_grad[i,f] = sum_k grad[m_k,f] * w[i,k]: one warp per hit, lanes over the features, k in order.
+__global__ void __launch_bounds__(256)
+push_grad_features_kernel(const float *__restrict__ grad, const float *__restrict__ weights,
+                          const int *__restrict__ nidx, float *__restrict__ feat_grad, int n_vert, int K, int F)
+{
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= n_vert) return;
+    for (int f = lane; f < F; f += 32) {
+        float acc = 0.f;
+        for (int k = 0; k < K; k++) {
+            const int m = nidx[(size_t)i * K + k];
+            if (m < 0 || m >= n_vert) continue;
+            acc = __fadd_rn(acc, __fmul_rn(grad[(size_t)m * F + f], weights[(size_t)i * K + k]));
+        }
+        feat_grad[(size_t)i * F + f] = acc;
+    }
+}
+
+// w_grad[i,k] = sum_f grad[m_k,f] * feat[i,f]: one thread per (hit, slot), f in order.
+__global__ void __launch_bounds__(256)
+push_grad_weights_kernel(const float *__restrict__ grad, const float *__restrict__ feat,
+                         const int *__restrict__ nidx, float *__restrict__ w_grad, long long n_edges,
+                         int n_vert, int K, int F)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_edges) return;
+    const int m = nidx[e];
+    float acc = 0.f;
+    if (m >= 0 && m < n_vert) {
+        const int i = (int)(e / K);
+        for (int f = 0; f < F; f++)
+            acc = __fadd_rn(acc, __fmul_rn(__ldg(grad + (size_t)m * F + f), feat[(size_t)i * F + f]));
+    }
+    w_grad[e] = acc;
+}
+
 }  // namespace
 }  // namespace hgc
 
 using namespace hgc;
+
+extern "C" int hgc_push_knn_grad(
+        const float *d_grad, const float *d_weights, const float *d_feat, const int *d_idxs,
+        float *d_feat_grad, float *d_w_grad, int n_vert, int n_neigh, int n_feat, hgc_stream_t stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n_vert < 0 || n_neigh < 0 || n_feat < 0) return HGC_ERR_INVALID_ARGUMENT;
+    if (n_vert == 0) return HGC_OK;
+    const long long ne = (long long)n_vert * n_neigh;
+    if (n_feat > 0 && (!d_grad || !d_feat || !d_feat_grad)) return HGC_ERR_INVALID_ARGUMENT;
+    if (ne > 0 && (!d_weights || !d_idxs || !d_w_grad)) return HGC_ERR_INVALID_ARGUMENT;
+    if (n_feat > 0) {
+        push_grad_features_kernel<<<div_up(n_vert, 8), 256, 0, stream>>>(d_grad, d_weights, d_idxs, d_feat_grad,
+                                                                        n_vert, n_neigh, n_feat);
+        HGC_LAUNCH_CHECK();
+    }
+    if (ne > 0) {
+        push_grad_weights_kernel<<<div_up(ne, 256), 256, 0, stream>>>(d_grad, d_feat, d_idxs, d_w_grad, ne, n_vert,
+                                                                     n_neigh, n_feat);
+        HGC_LAUNCH_CHECK();
+    }
+    return HGC_OK;
+}
 
 extern "C" int hgc_local_distance(
         const int *d_neigh_idxs, const float *d_coords, float *d_distances,

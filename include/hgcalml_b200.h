@@ -251,6 +251,12 @@ int hgc_local_distance(
 int hgc_push_knn(
         const float *d_weights, const float *d_feat, const int *d_idxs, float *d_out_feat,
         int n_vert, int n_neigh, int n_feat, void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+/* PushKnnGrad -- replaces PushKnnGradOpFunctor (modules/compiled/push_knn_grad_kernel.h; argument order as
+ * there): d_feat_grad[i,f] = sum_k d_grad[m_k,f] * d_weights[i,k], d_w_grad[i,k] = sum_f d_grad[m_k,f] *
+ * d_feat[i,f], both summed in order.  No workspace. */
+int hgc_push_knn_grad(
+        const float *d_grad, const float *d_weights, const float *d_feat, const int *d_idxs,
+        float *d_feat_grad, float *d_w_grad, int n_vert, int n_neigh, int n_feat, hgc_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -481,3 +481,33 @@ void oracle_push_knn(const float *weights, const float *feat, const int *nidx, f
             }
         }
 }
+
+/* ------------------------------------------------------------------------
+ * PushKnnGrad
+ * restates modules/compiled/push_knn_grad_kernel.cc:22-95:
+ *   feat_grad[i,f] = sum_k grad[m_k,f] * w[i,k]      (k ascending)
+ *   w_grad[i,k]    = sum_f grad[m_k,f] * feat[i,f]   (f ascending; 0 for padding)
+ * ---------------------------------------------------------------------- */
+void oracle_push_knn_grad(const float *grad, const float *weights, const float *feat, const int *nidx,
+                          float *feat_grad, float *w_grad, int n_vert, int n_neigh, int n_feat)
+{
+    for (int i = 0; i < n_vert; i++)
+        for (int f = 0; f < n_feat; f++) {
+            float acc = 0.f;
+            for (int k = 0; k < n_neigh; k++) {
+                const int m = nidx[(size_t)i * n_neigh + k];
+                if (m < 0) continue;
+                acc += grad[(size_t)m * n_feat + f] * weights[(size_t)i * n_neigh + k];
+            }
+            feat_grad[(size_t)i * n_feat + f] = acc;
+        }
+    for (int i = 0; i < n_vert; i++)
+        for (int k = 0; k < n_neigh; k++) {
+            const int m = nidx[(size_t)i * n_neigh + k];
+            float acc = 0.f;
+            if (m >= 0)
+                for (int f = 0; f < n_feat; f++)
+                    acc += grad[(size_t)m * n_feat + f] * feat[(size_t)i * n_feat + f];
+            w_grad[(size_t)i * n_neigh + k] = acc;
+        }
+}

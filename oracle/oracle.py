@@ -216,6 +216,19 @@ def op_push_knn(weights, features, indices, backend="port"):
     return out
 
 
+def op_push_knn_grad(grad, weights, features, indices, backend="port"):
+    """Functor of push_knn_grad_kernel.cc:22-95. Returns (weight_grad [N,K], feature_grad [N,F])."""
+    grad = _c32f(grad)
+    weights = _c32f(weights)
+    features = _c32f(features)
+    indices = _c32i(indices)
+    fg = np.zeros_like(features)
+    wg = np.zeros_like(weights)
+    lib(backend).fn("push_knn_grad")(_f(grad), _f(weights), _f(features), _i(indices), _f(fg), _f(wg),
+                                     c_int(features.shape[0]), c_int(indices.shape[1]), c_int(features.shape[1]))
+    return wg, fg
+
+
 def op_binned_assign_to_condensates(ccoords, dist, beta, mask, bins_flat, bin_splits,
                                     indices_to_filtered, original_indices_h, row_splits, n_bins,
                                     bin_width, ccoords_h, dist_h, beta_h, mask_h, row_splits_h,

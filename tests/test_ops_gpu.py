@@ -489,3 +489,19 @@ def test_local_distance_and_push_knn_vs_checker(cuda, oracle):
     g = load_golden("knn_showers4d")
     d2 = LocalDistance(T(g["coords"], cuda), T(g["idx"], cuda))
     assert np.array_equal(bits(N(d2)), bits(g["dist"]))
+
+
+def test_push_knn_grad_vs_checker_and_autograd(cuda, oracle):
+    from hgcalml_b200.push_knn_op import PushKnn, PushKnnGrad
+    rng = np.random.default_rng(33)
+    n, K, F = 4000, 12, 20
+    idx = rng.integers(-1, n, (n, K)).astype(np.int32)
+    w = rng.random((n, K), dtype=np.float32)
+    f = rng.standard_normal((n, F), dtype=np.float32)
+    g = rng.standard_normal((n, F), dtype=np.float32)
+    rw, rf = oracle.op_push_knn_grad(g, w, f, idx)
+    gw, gf = PushKnnGrad(T(g, cuda), T(w, cuda), T(f, cuda), T(idx, cuda))
+    assert np.array_equal(bits(N(gw)), bits(rw)) and np.array_equal(bits(N(gf)), bits(rf))
+    wt, ft = T(w, cuda).requires_grad_(True), T(f, cuda).requires_grad_(True)
+    (PushKnn(wt, ft, T(idx, cuda)) * T(g, cuda)).sum().backward()
+    assert torch.equal(wt.grad, gw) and torch.equal(ft.grad, gf)
