@@ -17,6 +17,7 @@
 // The reference finds a condensate's hits through the bins overlapping its bounding box and then
 // applies an exact distance test; testing all condensates of the event gives the same set, so the
 // bin inputs are accepted for interface compatibility and not read.
+#include <cooperative_groups.h>
 #include "common.cuh"
 
 namespace hgc {
@@ -93,12 +94,34 @@ __device__ __forceinline__ float centre_distsq(const float *c, const float *x, i
 }
 
 // Step 2.  order[] lists, per event, the subset positions in priority order.
-__global__ void __launch_bounds__(kClaimThreads)
+//
+// A cluster of kClusterBlocks blocks works on one event and walks the priority order in windows of
+// kWindow hits.  (a) Every block tests its 1024 hits of the window against the condensates confirmed
+// in earlier windows and leaves a flag per hit.  (b) After a cluster barrier, block 0 resolves the
+// survivors in order: the first open hit becomes the next condensate and closes the later survivors
+// it covers.  (c) A second cluster barrier publishes the longer condensate list to all blocks.
+// The barriers are the hardware cluster barrier; every block of a cluster runs the same number of
+// windows, so none can be left waiting.
+constexpr int kClusterBlocks = 8;
+constexpr int kWindow = kClusterBlocks * kClaimThreads;
+constexpr int kItems = kWindow / kClaimThreads;  // survivors a thread of block 0 looks after
+
+__device__ __forceinline__ bool covers(const float *c, float r2, int lonely, int c_pos, const float *x, int dims,
+                                       int x_pos, int x_mask)
+{
+    if (lonely) return c_pos == x_pos;
+    return x_mask == 0 && centre_distsq(c, x, dims) <= r2;
+}
+
+__global__ void __cluster_dims__(kClusterBlocks, 1, 1) __launch_bounds__(kClaimThreads)
 claim_kernel(int dims, const float *__restrict__ ccoords_h, const float *__restrict__ dist_h,
              const int *__restrict__ mask_h, const int *__restrict__ original_indices_h,
              const int *__restrict__ row_splits_h, const int *__restrict__ order,
-             int *__restrict__ status_h, int *__restrict__ alpha_indices, CondList cl)
+             int *__restrict__ status_h, int *__restrict__ alpha_indices, int *__restrict__ open_flags,
+             CondList cl)
 {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     __shared__ float s_c[kCondTile][kMaxDims];
     __shared__ float s_r2[kCondTile];
     __shared__ int s_pos[kCondTile];
@@ -108,83 +131,106 @@ claim_kernel(int dims, const float *__restrict__ ccoords_h, const float *__restr
     __shared__ float s_new_r2;
     __shared__ int s_new_pos, s_new_lonely;
 
-    const int e = blockIdx.x;
+    const int rank = (int)cluster.block_rank();
+    const int e = blockIdx.x / kClusterBlocks;
     const int off = row_splits_h[e], n_h = row_splits_h[e + 1] - off;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    int n_cond = 0;
+    int *flags = open_flags + (size_t)e * kWindow;
+    volatile int *count = cl.count + e;
 
-    for (int w0 = 0; w0 < n_h; w0 += kClaimThreads) {
-        const bool active = w0 + t < n_h;
+    for (int w0 = 0; w0 < n_h; w0 += kWindow) {
+        int n_cond = *count;  // published by block 0 before the barrier that ended the previous window
+
+        // (a) this block's hits of the window against the confirmed condensates
+        const int p = w0 + rank * kClaimThreads + t;
+        const bool active = p < n_h;
         int a = 0, my_mask = 0;
         float x[kMaxDims];
         if (active) {
-            a = order[off + w0 + t];
+            a = order[off + p];
             my_mask = mask_h[a];
 #pragma unroll
             for (int d = 0; d < kMaxDims; d++) x[d] = d < dims ? ccoords_h[(size_t)a * dims + d] : 0.f;
         }
-        bool open = active;  // neither claimed nor made a condensate yet
-
-        // (1) against the condensates confirmed in earlier windows
+        bool open = active;
         for (int c0 = 0; c0 < n_cond; c0 += kCondTile) {
             const int nt = min(kCondTile, n_cond - c0);
             __syncthreads();
             if (t < nt) {
-                for (int d = 0; d < dims; d++) s_c[t][d] = cl.centre[(size_t)(off + c0 + t) * dims + d];
-                s_r2[t] = cl.radius_sq[off + c0 + t];
-                s_pos[t] = cl.subset_pos[off + c0 + t];
-                s_lonely[t] = cl.lonely[off + c0 + t];
+                // written by block 0 on another SM during this launch: read past the (incoherent) L1
+                for (int d = 0; d < dims; d++) s_c[t][d] = __ldcg(cl.centre + (size_t)(off + c0 + t) * dims + d);
+                s_r2[t] = __ldcg(cl.radius_sq + off + c0 + t);
+                s_pos[t] = __ldcg(cl.subset_pos + off + c0 + t);
+                s_lonely[t] = __ldcg(cl.lonely + off + c0 + t);
             }
             __syncthreads();
             if (open) {
-                for (int c = 0; c < nt; c++) {
-                    bool covered;
-                    if (s_lonely[c]) covered = s_pos[c] == a;
-                    else covered = my_mask == 0 && centre_distsq(s_c[c], x, dims) <= s_r2[c];
-                    if (covered) { open = false; break; }
-                }
+                for (int c = 0; c < nt; c++)
+                    if (covers(s_c[c], s_r2[c], s_lonely[c], s_pos[c], x, dims, a, my_mask)) { open = false; break; }
             }
         }
+        __stcg(flags + rank * kClaimThreads + t, open ? 1 : 0);
+        __threadfence();
+        cluster.sync();
 
-        // (2) resolve the window's survivors in priority order
-        for (int guard = 0; guard <= kClaimThreads; guard++) {
-            const unsigned m = __ballot_sync(0xffffffffu, open);
-            __syncthreads();
-            if (lane == 0) s_first[warp] = m ? (warp * 32 + __ffs(m) - 1) : kClaimThreads;
-            __syncthreads();
-            int first = s_first[lane];
+        // (b) block 0: the survivors of the whole window, in priority order
+        if (rank == 0) {
+            unsigned open_bits = 0u;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
-            if (first >= kClaimThreads) break;
-            if (t == first) {
-                const float radius = dist_h[a];
-                const int lonely = my_mask > 0;
-                for (int d = 0; d < dims; d++) {
-                    s_new_c[d] = x[d];
-                    cl.centre[(size_t)(off + n_cond) * dims + d] = x[d];
+            for (int q = 0; q < kItems; q++)
+                if (__ldcg(flags + t * kItems + q)) open_bits |= 1u << q;
+            for (int guard = 0; guard <= kWindow; guard++) {
+                int first = open_bits ? t * kItems + __ffs(open_bits) - 1 : kWindow;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+                __syncthreads();
+                if (lane == 0) s_first[warp] = first;
+                __syncthreads();
+                first = s_first[lane];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+                if (first >= kWindow) break;
+                if (first / kItems == t) {
+                    const int pos = order[off + w0 + first];
+                    const float radius = dist_h[pos];
+                    const int lonely = mask_h[pos] > 0;
+                    for (int d = 0; d < dims; d++) {
+                        const float v = ccoords_h[(size_t)pos * dims + d];
+                        s_new_c[d] = v;
+                        cl.centre[(size_t)(off + n_cond) * dims + d] = v;
+                    }
+                    s_new_r2 = __fmul_rn(radius, radius);
+                    s_new_pos = pos;
+                    s_new_lonely = lonely;
+                    cl.radius_sq[off + n_cond] = __fmul_rn(radius, radius);
+                    cl.subset_pos[off + n_cond] = pos;
+                    cl.lonely[off + n_cond] = lonely;
+                    status_h[pos] = 1;
+                    alpha_indices[off + n_cond] = original_indices_h[pos];
+                    open_bits &= ~(1u << (first - t * kItems));
                 }
-                s_new_r2 = __fmul_rn(radius, radius);
-                s_new_pos = a;
-                s_new_lonely = lonely;
-                cl.radius_sq[off + n_cond] = __fmul_rn(radius, radius);
-                cl.subset_pos[off + n_cond] = a;
-                cl.lonely[off + n_cond] = lonely;
-                status_h[a] = 1;
-                alpha_indices[off + n_cond] = original_indices_h[a];
-                open = false;
+                __syncthreads();
+                unsigned todo = open_bits;
+                while (todo) {
+                    const int q = __ffs(todo) - 1;
+                    todo &= todo - 1;
+                    if (t * kItems + q < first) continue;
+                    const int pos = order[off + w0 + t * kItems + q];
+                    float y[kMaxDims];
+#pragma unroll
+                    for (int d = 0; d < kMaxDims; d++) y[d] = d < dims ? ccoords_h[(size_t)pos * dims + d] : 0.f;
+                    if (covers(s_new_c, s_new_r2, s_new_lonely, s_new_pos, y, dims, pos, mask_h[pos]))
+                        open_bits &= ~(1u << q);
+                }
+                n_cond++;
             }
             __syncthreads();
-            if (open && t > first) {
-                bool covered;
-                if (s_new_lonely) covered = s_new_pos == a;
-                else covered = my_mask == 0 && centre_distsq(s_new_c, x, dims) <= s_new_r2;
-                if (covered) open = false;
-            }
-            n_cond++;
+            if (t == 0) *count = n_cond;
+            __threadfence();
         }
-        __syncthreads();
+        // (c) the longer list becomes visible to all blocks of the cluster
+        cluster.sync();
     }
-    if (t == 0) cl.count[e] = n_cond;
 }
 
 __global__ void condensate_totals_kernel(const int *__restrict__ count, int num_rows,
@@ -289,7 +335,7 @@ using namespace hgc;
 
 namespace {
 struct CondBuffers {
-    int *beta_keys, *event_keys, *k1, *v1, *k2, *v2, *tk, *tv, *hist;
+    int *beta_keys, *event_keys, *k1, *v1, *k2, *v2, *tk, *tv, *hist, *open_flags;
     CondList cl;
 };
 template <typename W>
@@ -308,6 +354,7 @@ void cond_layout(W &ws, int n_h, int num_rows, int dims, CondBuffers *out)
     b.cl.subset_pos = ws.template take<int>(n);
     b.cl.lonely = ws.template take<int>(n);
     b.cl.count = ws.template take<int>(num_rows > 0 ? num_rows : 0);
+    b.open_flags = ws.template take<int>((size_t)(num_rows > 0 ? num_rows : 0) * kWindow);
     if (out) *out = b;
 }
 struct CondSizer {
@@ -373,10 +420,9 @@ extern "C" int hgc_binned_assign_to_condensates(
         gather_int_kernel<<<div_up(n_vert_h, 256), 256, 0, stream>>>(b.event_keys, b.v1, b.k1, n_vert_h);
         HGC_LAUNCH_CHECK();
         if (int rc = sort_pairs(b.k1, b.v1, b.k2, b.v2, b.tk, b.tv, b.hist, n_vert_h, bits_for(num_rows), stream)) return rc;
-        claim_kernel<<<num_rows, kClaimThreads, 0, stream>>>(dimensions, d_ccoords_h, d_dist_h,
-                                                             d_no_condensation_mask_h, d_original_indices_h,
-                                                             d_row_splits_h, b.v2, d_high_assigned_status_h,
-                                                             d_alpha_indices, b.cl);
+        claim_kernel<<<num_rows * kClusterBlocks, kClaimThreads, 0, stream>>>(
+                dimensions, d_ccoords_h, d_dist_h, d_no_condensation_mask_h, d_original_indices_h, d_row_splits_h,
+                b.v2, d_high_assigned_status_h, d_alpha_indices, b.open_flags, b.cl);
         HGC_LAUNCH_CHECK();
     }
     condensate_totals_kernel<<<1, 32, 0, stream>>>(b.cl.count, num_rows, d_n_condensates);
