@@ -44,6 +44,7 @@ def _load():
         "hgc_index_replacer": (I, [P, P, P, I, I, P, P]),
         "hgc_accumulate_knn": (I, [P] * 5 + [I] * 6 + [P]),
         "hgc_accumulate_knn_exp": (I, [P] * 5 + [I] * 5 + [ctypes.c_float, P, P]),
+        "hgc_gravnet_collect": (I, [P, P, I, I, I, P, P, I, P, I, I, ctypes.c_float, I, P, P]),
         "hgc_binned_select_knn_ragged_workspace_bytes": (S, [I] * 6),
         "hgc_binned_select_knn_ragged": (I, [P] * 6 + [I] * 8 + [P, S, P]),
         "hgc_local_distance": (I, [P, P, P, I, I, I, I, P]),

@@ -39,8 +39,8 @@ template <int LPH, int VPL, int CH, int MINB, bool EXP, bool WITH_ARG>
 __global__ void __launch_bounds__(kAccThreads, MINB)
 accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restrict__ feat,
                       const int *__restrict__ idxs, float *__restrict__ out, int *__restrict__ out_arg,
-                      int n_vert, int K, int F4, int n_out_feat, bool mean_and_max,
-                      const int *__restrict__ order, float scale)
+                      int n_vert, int K, int ldk, int F4, int n_out_feat, bool mean_and_max,
+                      const int *__restrict__ order, float scale, bool sub_self)
 {
     constexpr int kGroupsPerBlock = kAccThreads / LPH;
     static_assert(LPH % CH == 0 || CH > LPH, "chunking");
@@ -75,8 +75,8 @@ accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restric
         int next_j = -1;
         float next_w = 0.f;
         if (live && gl < K) {
-            next_j = idxs[(size_t)v * K + gl];
-            next_w = weights[(size_t)v * K + gl];
+            next_j = idxs[(size_t)v * ldk + gl];
+            next_w = weights[(size_t)v * ldk + gl];
         }
         for (int c0 = 0; c0 < K; c0 += LPH) {
             int my_j = next_j;
@@ -84,8 +84,8 @@ accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restric
             next_j = -1;
             next_w = 0.f;
             if (live && c0 + LPH + gl < K) {
-                next_j = idxs[(size_t)v * K + c0 + LPH + gl];
-                next_w = weights[(size_t)v * K + c0 + LPH + gl];
+                next_j = idxs[(size_t)v * ldk + c0 + LPH + gl];
+                next_w = weights[(size_t)v * ldk + c0 + LPH + gl];
             }
             if (my_j >= 0) {
                 if (EXP) my_w = expf(-__fmul_rn(scale, my_w));
@@ -171,10 +171,17 @@ accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restric
                 m.y = __fdiv_rn(sum[u].y, inv_count);
                 m.z = __fdiv_rn(sum[u].z, inv_count);
                 m.w = __fdiv_rn(sum[u].w, inv_count);
+                float4 mx = best[u];
+                if (sub_self) {
+                    // the hit's own row is taken off the mean and the max (one rounding each)
+                    const float4 own = __ldg(feat + (size_t)v * F4 + vec);
+                    m = make_float4(__fsub_rn(m.x, own.x), __fsub_rn(m.y, own.y), __fsub_rn(m.z, own.z), __fsub_rn(m.w, own.w));
+                    mx = make_float4(__fsub_rn(mx.x, own.x), __fsub_rn(mx.y, own.y), __fsub_rn(mx.z, own.z), __fsub_rn(mx.w, own.w));
+                }
                 float4 *row = reinterpret_cast<float4 *>(out + (size_t)v * n_out_feat);
                 __stcs(row + vec, m);  // results are written once and not read again by this kernel
                 if (mean_and_max) {
-                    __stcs(row + F4 + vec, best[u]);
+                    __stcs(row + F4 + vec, mx);
                     if (WITH_ARG) __stcs(reinterpret_cast<int4 *>(out_arg + (size_t)v * F4 * 4) + vec, arg[u]);
                 }
             }
@@ -187,8 +194,8 @@ template <bool EXP>
 __global__ void __launch_bounds__(kAccThreads)
 accumulate_scalar_kernel(const float *__restrict__ weights, const float *__restrict__ feat,
                          const int *__restrict__ idxs, float *__restrict__ out, int *__restrict__ out_arg,
-                         int n_vert, int K, int F, int n_out_feat, bool mean_and_max,
-                         const int *__restrict__ order, float scale)
+                         int n_vert, int K, int ldk, int F, int n_out_feat, bool mean_and_max,
+                         const int *__restrict__ order, float scale, bool sub_self)
 {
     const int lane = threadIdx.x & 31;
     const int warps_per_block = kAccThreads / kWarp;
@@ -199,15 +206,21 @@ accumulate_scalar_kernel(const float *__restrict__ weights, const float *__restr
             float sum = 0.f, best = 0.f;
             int arg = 0;
             for (int s = 0; s < K; s++) {
-                const int j = idxs[(size_t)v * K + s];
+                const int j = idxs[(size_t)v * ldk + s];
                 if (j < 0 || j >= n_vert) continue;
-                float w = weights[(size_t)v * K + s];
+                float w = weights[(size_t)v * ldk + s];
                 if (EXP) w = expf(-__fmul_rn(scale, w));
                 const float t = __fmul_rn(feat[(size_t)j * F + f], w);
                 sum = __fadd_rn(sum, t);
                 if (t >= best || s == 0) { best = t; arg = j; }
             }
-            out[(size_t)v * n_out_feat + f] = __fdiv_rn(sum, (float)K);
+            float mean = __fdiv_rn(sum, (float)K);
+            if (sub_self) {
+                const float own = feat[(size_t)v * F + f];
+                mean = __fsub_rn(mean, own);
+                best = __fsub_rn(best, own);
+            }
+            out[(size_t)v * n_out_feat + f] = mean;
             if (mean_and_max) {
                 out[(size_t)v * n_out_feat + F + f] = best;
                 if (out_arg) out_arg[(size_t)v * F + f] = arg;
@@ -218,8 +231,8 @@ accumulate_scalar_kernel(const float *__restrict__ weights, const float *__restr
 
 template <int LPH, int VPL, int CH, int MINB>
 int launch_vec(bool exp_w, bool with_arg, const float *w, const float *feat, const int *idxs, float *out,
-               int *out_arg, int n_vert, int K, int F4, int n_out, bool mm, const int *order,
-               float scale, cudaStream_t stream)
+               int *out_arg, int n_vert, int K, int ldk, int F4, int n_out, bool mm, const int *order,
+               float scale, bool sub_self, cudaStream_t stream)
 {
     long long blocks = div_up(n_vert, kAccTile);
     const long long cap = (long long)kNumSMs * 32;
@@ -227,7 +240,7 @@ int launch_vec(bool exp_w, bool with_arg, const float *w, const float *feat, con
     const float4 *f4 = reinterpret_cast<const float4 *>(feat);
 #define HGC_GO(E, A)                                                                              \
     accumulate_vec_kernel<LPH, VPL, CH, MINB, E, A><<<(int)blocks, kAccThreads, 0, stream>>>(     \
-            w, f4, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale)
+            w, f4, idxs, out, out_arg, n_vert, K, ldk, F4, n_out, mm, order, scale, sub_self)
     if (exp_w) { if (with_arg) HGC_GO(true, true); else HGC_GO(true, false); }
     else       { if (with_arg) HGC_GO(false, true); else HGC_GO(false, false); }
 #undef HGC_GO
@@ -235,18 +248,20 @@ int launch_vec(bool exp_w, bool with_arg, const float *w, const float *feat, con
     return HGC_OK;
 }
 
+// ldk: row stride of the weight and index arrays (>= K); ld_out: row stride of the output.
 int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int *idxs, float *out,
-                        int *out_arg, int n_vert, int K, int F, int n_out, int mean_and_max,
-                        const int *order, float scale, cudaStream_t stream)
+                        int *out_arg, int n_vert, int K, int ldk, int F, int ld_out, int mean_and_max,
+                        const int *order, float scale, bool sub_self, cudaStream_t stream)
 {
-    if (n_vert < 0 || K < 0 || F < 0) return HGC_ERR_INVALID_ARGUMENT;
-    if (n_out != (mean_and_max ? 2 * F : F)) return HGC_ERR_INVALID_ARGUMENT;
+    if (n_vert < 0 || K < 0 || F < 0 || ldk < K) return HGC_ERR_INVALID_ARGUMENT;
+    if (ld_out < (mean_and_max ? 2 * F : F)) return HGC_ERR_INVALID_ARGUMENT;
     if (n_vert == 0 || F == 0) return HGC_OK;
     if (!feat || !out || (K > 0 && (!w || !idxs))) return HGC_ERR_INVALID_ARGUMENT;
+    const int n_out = ld_out;
     const bool mm = mean_and_max != 0;
     const bool with_arg = mm && out_arg != nullptr;
     auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    const bool vec_ok = (F % 4 == 0) && F <= 512 && aligned16(feat) && aligned16(out) &&
+    const bool vec_ok = (F % 4 == 0) && (ld_out % 4 == 0) && F <= 512 && aligned16(feat) && aligned16(out) &&
                         (!with_arg || aligned16(out_arg));
     if (!vec_ok) {
         long long blocks = div_up(n_vert, kAccThreads / kWarp);
@@ -254,15 +269,15 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
         if (blocks > cap) blocks = cap;
         if (exp_w)
             accumulate_scalar_kernel<true><<<(int)blocks, kAccThreads, 0, stream>>>(
-                    w, feat, idxs, out, with_arg ? out_arg : nullptr, n_vert, K, F, n_out, mm, order, scale);
+                    w, feat, idxs, out, with_arg ? out_arg : nullptr, n_vert, K, ldk, F, n_out, mm, order, scale, sub_self);
         else
             accumulate_scalar_kernel<false><<<(int)blocks, kAccThreads, 0, stream>>>(
-                    w, feat, idxs, out, with_arg ? out_arg : nullptr, n_vert, K, F, n_out, mm, order, scale);
+                    w, feat, idxs, out, with_arg ? out_arg : nullptr, n_vert, K, ldk, F, n_out, mm, order, scale, sub_self);
         HGC_LAUNCH_CHECK();
         return HGC_OK;
     }
     const int F4 = F / 4;
-#define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, F4, n_out, mm, order, scale, stream)
+#define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, ldk, F4, n_out, mm, order, scale, sub_self, stream)
     if (F4 <= 4) HGC_VEC(4, 1, 4, 3);
     if (F4 <= 8) HGC_VEC(8, 1, 4, 3);
     // F = 64: 16 lanes per hit, 4 rows in flight, 64 registers (4 blocks per SM) measured best of
@@ -284,8 +299,9 @@ extern "C" int hgc_accumulate_knn(
         hgc_stream_t stream)
 {
     (void)n_moments;  // read and ignored by the reference too (accumulate_knn_kernel.cc:44)
+    if (n_out_feat != (mean_and_max ? 2 * n_feat : n_feat)) return HGC_ERR_INVALID_ARGUMENT;
     return hgc::accumulate_dispatch(false, d_weights, d_feat, d_idxs, d_out_feat, d_out_maxidxs, n_vert,
-                                    n_neigh, n_feat, n_out_feat, mean_and_max, nullptr, 1.f,
+                                    n_neigh, n_neigh, n_feat, n_out_feat, mean_and_max, nullptr, 1.f, false,
                                     static_cast<cudaStream_t>(stream));
 }
 
@@ -295,7 +311,22 @@ extern "C" int hgc_accumulate_knn_exp(
         int n_vert, int n_neigh, int n_feat, int n_out_feat, int mean_and_max,
         float distance_scale, const int *d_order, hgc_stream_t stream)
 {
+    if (n_out_feat != (mean_and_max ? 2 * n_feat : n_feat)) return HGC_ERR_INVALID_ARGUMENT;
     return hgc::accumulate_dispatch(true, d_distances, d_feat, d_idxs, d_out_feat, d_out_maxidxs, n_vert,
-                                    n_neigh, n_feat, n_out_feat, mean_and_max, d_order, distance_scale,
-                                    static_cast<cudaStream_t>(stream));
+                                    n_neigh, n_neigh, n_feat, n_out_feat, mean_and_max, d_order, distance_scale,
+                                    false, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hgc_gravnet_collect(
+        const float *d_distances, const int *d_idxs, int ld_neigh, int first_slot, int n_neigh,
+        const float *d_feat, float *d_out, int ld_out, int *d_out_maxidxs,
+        int n_vert, int n_feat, float distance_scale, int subtract_self, const int *d_order,
+        hgc_stream_t stream)
+{
+    if (first_slot < 0 || n_neigh < 0 || ld_neigh < first_slot + n_neigh) return HGC_ERR_INVALID_ARGUMENT;
+    if (n_vert > 0 && n_neigh > 0 && (!d_distances || !d_idxs)) return HGC_ERR_INVALID_ARGUMENT;
+    return hgc::accumulate_dispatch(true, d_distances ? d_distances + first_slot : nullptr, d_feat,
+                                    d_idxs ? d_idxs + first_slot : nullptr, d_out, d_out_maxidxs, n_vert,
+                                    n_neigh, ld_neigh, n_feat, ld_out, 1, d_order, distance_scale,
+                                    subtract_self != 0, static_cast<cudaStream_t>(stream));
 }

@@ -159,6 +159,26 @@ int hgc_accumulate_knn_exp(
         int n_vert, int n_neigh, int n_feat, int n_out_feat, int mean_and_max,
         float distance_scale, const int *d_order, hgc_stream_t stream);
 
+/* The neighbour-collection step of the GravNet layers in one call
+ * (modules/GravNetLayersRagged.py:3195-3204 RaggedGravNet.create_output_features and :3587-3600
+ * DistanceWeightedMessagePassing.create_output_features): the layers slice the self slot off the
+ * kNN output (idx[:,1:], dist[:,1:], :3260), call AccumulateKnn(10.*distsq, features, idx) and take
+ * the hit's own features off both halves (features -= tile(prev_feat,[1,2])) before concatenating.
+ * Here the slice is an offset and a row stride, the weighting and the subtraction happen in the
+ * accumulation kernel, and the result lands in its columns of the caller's concatenation buffer:
+ *   d_distances, d_idxs [n_vert, ld_neigh]: slots first_slot .. first_slot+n_neigh-1 are used
+ *   d_feat [n_vert, n_feat]
+ *   d_out: first of 2*n_feat output columns (mean | max) of a row-major buffer with row stride
+ *          ld_out floats
+ *   d_out_maxidxs [n_vert, n_feat] or NULL
+ *   subtract_self != 0: out[v, f] -= feat[v, f] and out[v, n_feat+f] -= feat[v, f] (one rounding each,
+ *          applied to the rounded mean and max, as the separate TF subtraction does). */
+int hgc_gravnet_collect(
+        const float *d_distances, const int *d_idxs, int ld_neigh, int first_slot, int n_neigh,
+        const float *d_feat, float *d_out, int ld_out, int *d_out_maxidxs,
+        int n_vert, int n_feat, float distance_scale, int subtract_self, const int *d_order,
+        hgc_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * BinnedSelectKnn, wrapper level -- replaces the whole Python function BinnedSelectKnn
  * (modules/binned_select_knn_op.py:32-95: BinByCoordinates + argsort + gathers + the op +

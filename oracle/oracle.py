@@ -351,6 +351,65 @@ def AccumulateLinKnn(weights, features, indices, mean_and_max=True, backend="por
     return op_accumulate_knn(weights, features, indices, mean_and_max, backend)
 
 
+_NP_ACT = {
+    None: lambda t: t,
+    "linear": lambda t: t,
+    "relu": lambda t: np.maximum(t, np.float32(0.)),
+    "tanh": np.tanh,
+}
+
+
+def _np_dense(x, weights, activation):
+    """tf.keras.layers.Dense in float32: activation(x @ kernel [+ bias])."""
+    y = _c32f(x) @ _c32f(weights[0])
+    if len(weights) > 1:
+        y = y + _c32f(weights[1])
+    return _NP_ACT[activation](y).astype(np.float32)
+
+
+def gravnet_collect(features, neighbour_indices, distancesq, backend="port"):
+    """The collection step shared by the GravNet layers (modules/GravNetLayersRagged.py:3199-3202 with
+    :3264-3270, and :3594-3597 with :3602-3609): AccumulateKnn(10.*distsq, features, idx), reshaped
+    to [N, 2F], minus tile(features, [1, 2])."""
+    features = _c32f(features)
+    f, _ = AccumulateKnn(np.float32(10.) * _c32f(distancesq), features, neighbour_indices, backend=backend)
+    f = f.reshape(-1, features.shape[1] * 2)
+    return (f - np.tile(features, [1, 2])).astype(np.float32)
+
+
+def RaggedGravNet(x, row_splits, weights, n_neighbours, n_knn_bins=None, feature_activation="relu",
+                  return_self=True, dense=_np_dense, backend="port"):
+    """Forward pass of RaggedGravNet (modules/GravNetLayersRagged.py:3206-3224 with :3195-3204 and
+    :3246-3261).  weights = [[kernel, bias] of input_feature_transform, [kernel] of
+    input_spatial_transform, [kernel, bias] of output_feature_transform]; `dense(x, weights, activation)`
+    evaluates one dense layer (numpy by default; a test may hand in the very GEMM the other side uses so
+    that only the ops are compared)."""
+    x = _c32f(x)
+    coordinates = dense(x, weights[1], None)
+    idx, dist = BinnedSelectKnn(n_neighbours + 1, coordinates, row_splits, n_bins=n_knn_bins, backend=backend)
+    dist = np.where(idx < 0, np.float32(0.), dist).astype(np.float32)
+    nidx, ndist = idx[:, 1:], dist[:, 1:]
+    features = dense(x, weights[0], feature_activation)
+    collected = gravnet_collect(features, nidx, ndist, backend)
+    out = dense(np.concatenate([collected, x], axis=-1), weights[2], "relu")
+    if return_self:
+        return out, coordinates, idx, dist
+    return out, coordinates, nidx, ndist
+
+
+def DistanceWeightedMessagePassing(x, neighbour_indices, distancesq, weights, activation="relu",
+                                   dense=_np_dense, backend="port"):
+    """modules/GravNetLayersRagged.py:3587-3600; weights = [[kernel, bias], ...] per pass."""
+    x = _c32f(x)
+    allfeat = []
+    features = x
+    for w in weights:
+        prev_feat = dense(features, w, activation)
+        features = gravnet_collect(prev_feat, neighbour_indices, distancesq, backend)
+        allfeat.append(features)
+    return np.concatenate(allfeat + [x], axis=-1)
+
+
 def _segment_ids_to_row_splits(ids, num_segments):
     counts = np.bincount(ids, minlength=num_segments).astype(np.int64)
     return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)

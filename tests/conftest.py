@@ -22,6 +22,7 @@ def load_golden(name):
         base = load_golden(str(g.pop("base")))
         g.setdefault("feats", base["feats"])
         g.setdefault("idx", base["idx"])
+        g.setdefault("dist", base["dist"])
     return g
 
 

@@ -79,6 +79,15 @@ def main():
                                 maxidx=maxidx, grad_out=grad_out, grad_weights=gw, grad_feats=gf)
             print(name, gw.shape, gf.shape)
 
+    # the GravNet layers' collection step on the neighbour rows of two golden kNN cases: self slot
+    # sliced off, AccumulateKnn(10 d^2), own features subtracted (modules/GravNetLayersRagged.py:3199-3202)
+    for base in ("knn_showers4d", "knn_showers4d_tfcompat", "knn_uniform3d"):
+        case = dict(np.load(os.path.join(OUT, base + ".npz")))
+        collected = O.gravnet_collect(case["feats"], case["idx"][:, 1:], case["dist"][:, 1:], backend=BACKEND)
+        np.savez_compressed(os.path.join(OUT, "gravnet_collect_" + base[4:] + ".npz"), base=np.array(base),
+                            collected=collected)
+        print("gravnet_collect", base, collected.shape)
+
     # bin_by_coordinates op outputs
     c, _, rs = synth.shower_batch([400, 0, 650], dims=3, n_feat=1, seed=77)
     binass, flat, nb, bw, nper = O.BinByCoordinates(c, rs, n_bins=6, backend=BACKEND)

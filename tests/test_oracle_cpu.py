@@ -180,3 +180,28 @@ def test_keep_noise_invariants(oracle):
         assert np.array_equal(asso[al], al)
         a = assignment[rs[e]:rs[e + 1], 0]
         assert a.max() + 1 == len(al)
+
+
+@pytest.mark.parametrize("name", ["showers4d", "showers4d_tfcompat", "uniform3d"])
+def test_port_matches_golden_gravnet_collect(oracle, name):
+    g = load_golden("gravnet_collect_" + name)
+    got = oracle.gravnet_collect(g["feats"], g["idx"][:, 1:], g["dist"][:, 1:], backend="port")
+    assert np.array_equal(bits(got), bits(g["collected"]))
+
+
+def test_gravnet_layer_restatements_shapes(oracle):
+    """The numpy restatements of RaggedGravNet / DistanceWeightedMessagePassing: output layout."""
+    c, f, rs = synth.shower_batch([300, 0, 450], dims=4, n_feat=10, seed=3)
+    rng = np.random.default_rng(4)
+    w = [[rng.standard_normal((10, 6), dtype=np.float32), rng.standard_normal(6, dtype=np.float32)],
+         [rng.standard_normal((10, 3), dtype=np.float32)],
+         [rng.standard_normal((22, 7), dtype=np.float32), rng.standard_normal(7, dtype=np.float32)]]
+    out, coords, idx, dist = oracle.RaggedGravNet(f, rs, w, n_neighbours=8)
+    assert out.shape == (750, 7) and coords.shape == (750, 3) and idx.shape == dist.shape == (750, 9)
+    assert (idx[:, 0] == np.arange(750)).all() and (out >= 0).all()
+    out2, _, idx2, _ = oracle.RaggedGravNet(f, rs, w, n_neighbours=8, return_self=False)
+    assert np.array_equal(out, out2) and np.array_equal(idx2, idx[:, 1:])
+    wm = [[rng.standard_normal((10, 4), dtype=np.float32), rng.standard_normal(4, dtype=np.float32)],
+          [rng.standard_normal((8, 5), dtype=np.float32), rng.standard_normal(5, dtype=np.float32)]]
+    mp = oracle.DistanceWeightedMessagePassing(f, idx[:, 1:], dist[:, 1:], wm)
+    assert mp.shape == (750, 2 * (4 + 5) + 10) and np.array_equal(mp[:, 18:], f)
