@@ -47,6 +47,8 @@ def _load():
         "hgc_gravnet_collect": (I, [P, P, I, I, I, P, P, I, P, I, I, ctypes.c_float, I, P, P]),
         "hgc_binned_select_knn_ragged_workspace_bytes": (S, [I] * 6),
         "hgc_binned_select_knn_ragged": (I, [P] * 6 + [I] * 8 + [P, S, P]),
+        "hgc_build_and_assign_condensates_workspace_bytes": (S, [I] * 4),
+        "hgc_build_and_assign_condensates": (I, [P] * 11 + [I] * 3 + [ctypes.c_float] * 2 + [I] * 2 + [P, S, P]),
         "hgc_local_distance": (I, [P, P, P, I, I, I, I, P]),
         "hgc_push_knn": (I, [P, P, P, P, I, I, I, P, S, P]),
         "hgc_push_knn_grad": (I, [P] * 6 + [I] * 3 + [P]),

@@ -1,6 +1,7 @@
 """Host-side mirror of HGCalML's ``modules/assign_condensate_op.py`` on torch CUDA tensors."""
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -90,9 +91,50 @@ def BuildAndAssignCondensatesBinned(ccoords, betas, dist, row_splits, beta_thres
     """modules/assign_condensate_op.py:210-373.
 
     Returns ``assignment [N,1], association [N], alpha_idx, is_cond [N,1], n_condensates`` with the
-    reference's meaning.  The tensor glue around the op (binning, stable sort by bin, high-beta
-    filter, mapping back, and the ``keep_noise`` renumbering) follows the reference line by line on
-    CUDA tensors; the op itself is the library's parallel claim pass."""
+    reference's meaning.  Everything up to ``keep_noise`` is one library call
+    (``hgc_build_and_assign_condensates``: threshold scaling, shift, binning, stable sort by bin,
+    high-beta filter, the op, mapping back); the ``keep_noise`` renumbering runs as tensor ops."""
+    assert 1 <= nbin_dims <= 6
+    assert 0. <= beta_threshold <= 1.
+    assert distance_threshold > 0.
+    ccoords = C.f32(ccoords)
+    C.require_cuda(ccoords)
+    dev = ccoords.device
+    n, dims = ccoords.shape
+    betas = C.f32(betas, dev).reshape(-1)
+    dist = C.f32(dist, dev).reshape(-1)
+    row_splits = C.i32(row_splits, dev)
+    n_rs = row_splits.shape[0]
+    if betas.shape[0] != n or dist.shape[0] != n:
+        raise C.HgcError("BuildAndAssignCondensatesBinned: ccoords, betas and dist must have one row per hit")
+    mask = None
+    if no_condensation_mask is not None:
+        mask = C.i32(no_condensation_mask, dev).reshape(-1)
+    assignment = torch.empty((n,), dtype=torch.int32, device=dev)
+    asso = torch.empty((n,), dtype=torch.int32, device=dev)
+    alpha = torch.empty((n,), dtype=torch.int32, device=dev)
+    is_cond = torch.empty((n,), dtype=torch.uint8, device=dev)
+    n_condensates = torch.empty((n_rs,), dtype=torch.int32, device=dev)
+    ws = C.workspace(C.lib.hgc_build_and_assign_condensates_workspace_bytes(n, dims, n_rs, nbin_dims), dev)
+    n_alpha = ctypes.c_int(0)
+    C.check(C.lib.hgc_build_and_assign_condensates(
+        C.ptr(ccoords), C.ptr(betas), C.ptr(dist), C.ptr(mask), C.ptr(row_splits),
+        C.ptr(assignment), C.ptr(asso), C.ptr(alpha), C.ptr(is_cond), C.ptr(n_condensates),
+        ctypes.addressof(n_alpha), n, dims, n_rs, float(beta_threshold), float(distance_threshold),
+        int(bool(assign_by_max_beta)), nbin_dims, C.ptr(ws), ws.numel(), C.stream_of(ccoords)),
+        "BuildAndAssignCondensatesBinned")
+    out = (assignment[:, None], asso, alpha[:n_alpha.value], is_cond.to(torch.bool)[:, None], n_condensates)
+    if keep_noise:
+        out = merge_noise_as_indiv_cp(*out, row_splits)
+    return out
+
+
+def BuildAndAssignCondensatesBinnedStepwise(ccoords, betas, dist, row_splits, beta_threshold,
+                                            no_condensation_mask=None, distance_threshold=1.,
+                                            assign_by_max_beta=False, nbin_dims=3, keep_noise=False):
+    """The same function with the reference's tensor glue (modules/assign_condensate_op.py:245-310)
+    spelled out step by step on CUDA tensors around the registered op ``_BinnedAssignToCondensates``;
+    kept as the readable statement of what the one-call version does."""
     assert 1 <= nbin_dims <= 6
     assert 0. <= beta_threshold <= 1.
     assert distance_threshold > 0.

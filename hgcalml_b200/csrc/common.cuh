@@ -79,6 +79,10 @@ int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_
                int *keys_tmp, int *vals_tmp, int *block_hist, int n, int key_bits,
                cudaStream_t stream);
 
+// Exclusive prefix sum of `len` ints in place; tile_sums needs scan_scratch_ints(len) ints.
+size_t scan_scratch_ints(int len);
+int exclusive_scan_ints(int *data, int len, int *tile_sums, cudaStream_t stream);
+
 // bin_boundaries[b] = first position in the ascending key array whose key is >= b, for b in
 // [0, n_bins]; keys >= n_bins (sentinels) sort last and are not counted.
 int boundaries_from_sorted_keys(const int *sorted_keys, int n, int *bin_boundaries, int n_bins,

@@ -218,7 +218,27 @@ __global__ void fill_int_kernel(int *__restrict__ p, int n, int v)
 size_t sort_hist_ints(int n)
 {
     const size_t table = (size_t)kDigits * (size_t)div_up(n > 0 ? n : 1, kTile);
-    return table + (table + kScanTile - 1) / kScanTile + 1;  // digit table + its tile totals
+    return table + scan_scratch_ints((int)table);  // digit table + its tile totals
+}
+
+size_t scan_scratch_ints(int len) { return (size_t)div_up(len > 0 ? len : 1, kScanTile) + 1; }
+
+int exclusive_scan_ints(int *data, int len, int *tile_sums, cudaStream_t stream)
+{
+    if (len <= 0) return HGC_OK;
+    if (len <= 4 * kScanTile) {
+        scan_hist_kernel<<<1, 1024, 0, stream>>>(data, len);
+        HGC_LAUNCH_CHECK();
+        return HGC_OK;
+    }
+    const int n_tiles = div_up(len, kScanTile);
+    scan_tiles_kernel<<<n_tiles, 1024, 0, stream>>>(data, len, tile_sums);
+    HGC_LAUNCH_CHECK();
+    scan_hist_kernel<<<1, 1024, 0, stream>>>(tile_sums, n_tiles);
+    HGC_LAUNCH_CHECK();
+    add_tile_offsets_kernel<<<div_up(len, 256), 256, 0, stream>>>(data, len, tile_sums);
+    HGC_LAUNCH_CHECK();
+    return HGC_OK;
 }
 
 int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_out,
@@ -239,19 +259,7 @@ int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_
         digit_count_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, n, shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();
         const int table = kDigits * n_blocks;
-        if (table <= 4 * kScanTile) {
-            scan_hist_kernel<<<1, 1024, 0, stream>>>(block_hist, table);
-            HGC_LAUNCH_CHECK();
-        } else {
-            const int n_tiles = div_up(table, kScanTile);
-            int *tile_sums = block_hist + table;
-            scan_tiles_kernel<<<n_tiles, 1024, 0, stream>>>(block_hist, table, tile_sums);
-            HGC_LAUNCH_CHECK();
-            scan_hist_kernel<<<1, 1024, 0, stream>>>(tile_sums, n_tiles);
-            HGC_LAUNCH_CHECK();
-            add_tile_offsets_kernel<<<div_up(table, 256), 256, 0, stream>>>(block_hist, table, tile_sums);
-            HGC_LAUNCH_CHECK();
-        }
+        if (int rc = exclusive_scan_ints(block_hist, table, block_hist + table, stream)) return rc;
         digit_scatter_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, src_v, kbuf[dst], vbuf[dst], n,
                                                                     shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();

@@ -220,6 +220,32 @@ int hgc_binned_assign_to_condensates(
         const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, int assign_by_max_beta,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream);
 
+/* BuildAndAssignCondensatesBinned, wrapper level -- the Python function of
+ * modules/assign_condensate_op.py:210-310 up to (not including) keep_noise: dist / distance_threshold,
+ * ccoords -= min over the batch, BinByCoordinates on the first nbin_dims coordinates with
+ * n_bins_sc = max(4, min(ceil((n_vert/5)^(1/3)), 25)), stable sort by bin, gathers, the high-beta
+ * filter (betas > beta_threshold or mask > 0) with indices_to_filtered / original_indices /
+ * row_splits_h, the op, the mapping back to the caller's order, alpha_indices[alpha_indices != -1]
+ * and the condensate flags.
+ *   inputs, caller's order: d_ccoords [n_vert, dimensions], d_betas, d_dist [n_vert],
+ *          d_no_condensation_mask [n_vert] or NULL, d_row_splits [n_rs] (spanning 0 .. n_vert)
+ *   outputs: d_assignment, d_association [n_vert]; d_alpha_idx [n_vert]: the condensates' hit ids,
+ *          event by event, -1 after the last; d_is_cond [n_vert] bytes (0 / 1);
+ *          d_n_condensates [n_rs] cumulative count
+ *   h_n_alpha (host, may be NULL): receives the number of condensates; the call then returns after
+ *          the stream has finished.
+ * The number of high-beta hits sizes the op's filtered inputs and is read back once in the middle
+ * of the call (one stream synchronisation; the reference's boolean masks do the same). */
+size_t hgc_build_and_assign_condensates_workspace_bytes(int n_vert, int dimensions, int n_rs, int nbin_dims);
+int hgc_build_and_assign_condensates(
+        const float *d_ccoords, const float *d_betas, const float *d_dist, const int *d_no_condensation_mask,
+        const int *d_row_splits,
+        int *d_assignment, int *d_association, int *d_alpha_idx, unsigned char *d_is_cond,
+        int *d_n_condensates, int *h_n_alpha,
+        int n_vert, int dimensions, int n_rs, float beta_threshold, float distance_threshold,
+        int assign_by_max_beta, int nbin_dims,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * Backward ops (registered as the gradients of AccumulateKnn and BinnedSelectKnn:
  * modules/accknn_op.py:71-90, modules/binned_select_knn_op.py:107-118).

@@ -505,3 +505,35 @@ def test_push_knn_grad_vs_checker_and_autograd(cuda, oracle):
     wt, ft = T(w, cuda).requires_grad_(True), T(f, cuda).requires_grad_(True)
     (PushKnn(wt, ft, T(idx, cuda)) * T(g, cuda)).sum().backward()
     assert torch.equal(wt.grad, gw) and torch.equal(ft.grad, gf)
+
+
+@pytest.mark.parametrize("dims,nbin_dims,thr", [(3, 3, 1.0), (2, 3, 0.7), (4, 2, 1.3), (3, 1, 0.5)])
+def test_condensates_one_call_equals_stepwise_and_checker(cuda, oracle, dims, nbin_dims, thr):
+    """The one-call wrapper, the stepwise tensor-op wrapper around the op, and the checker agree
+    bit for bit, with a distance threshold, fewer binned dimensions, a mask and empty events."""
+    from hgcalml_b200.assign_condensate_op import (BuildAndAssignCondensatesBinned,
+                                                   BuildAndAssignCondensatesBinnedStepwise)
+    cc, beta, _ = synth.condensation_batch(3, 6000, 40, dims, 0.1, seed=420 + dims)
+    rs = np.array([0, 6000, 6000, 12000, 18000, 18000], np.int32)  # two empty events
+    rng = np.random.default_rng(5)
+    d = rng.uniform(0.2, 0.6, beta.shape).astype(np.float32)
+    mask = (rng.random(beta.shape) < 0.02).astype(np.int32)
+    for amb in (True, False):
+        for m in (None, mask):
+            kw = dict(distance_threshold=thr, assign_by_max_beta=amb, nbin_dims=nbin_dims)
+            ref = oracle.BuildAndAssignCondensatesBinned(cc, beta, d, rs, 0.1, no_condensation_mask=m, **kw)
+            mt = None if m is None else T(m, cuda)
+            args = (T(cc, cuda), T(beta, cuda), T(d, cuda), T(rs, cuda), 0.1)
+            one = BuildAndAssignCondensatesBinned(*args, no_condensation_mask=mt, **kw)
+            step = BuildAndAssignCondensatesBinnedStepwise(*args, no_condensation_mask=mt, **kw)
+            for r, a, b, key in zip(ref, one, step, COND_KEYS):
+                assert np.array_equal(N(a), r), key
+                assert np.array_equal(N(b), r), key
+                assert a.dtype == b.dtype and a.shape == b.shape, key
+
+
+def test_condensates_one_call_empty_batch(cuda):
+    from hgcalml_b200.assign_condensate_op import BuildAndAssignCondensatesBinned
+    z = torch.zeros((0, 3), device=cuda)
+    out = BuildAndAssignCondensatesBinned(z, z[:, :1], z[:, :1], torch.zeros(3, dtype=torch.int32, device=cuda), 0.1)
+    assert out[0].shape == (0, 1) and out[2].numel() == 0 and N(out[4]).tolist() == [0, 0, 0]
