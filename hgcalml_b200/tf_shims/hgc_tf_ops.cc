@@ -280,6 +280,108 @@ private:
     bool assign_by_max_beta_;
 };
 
+// ------------------------------------------------------------------ wrapper-level ops
+// These have no counterpart among the reference's registered ops: each replaces the TensorFlow glue
+// of a Python wrapper together with the op inside it, so the wrapper shrinks to one op call.
+
+// BinnedSelectKnn of modules/binned_select_knn_op.py:32-95 (binning, argsort, gathers, the op,
+// IndexReplacer, scatter back) in one enqueue.  n_bins <= 0 selects the wrapper's default.
+class HgcBinnedSelectKnnRaggedGpuOp : public OpKernel {
+public:
+    explicit HgcBinnedSelectKnnRaggedGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("n_neighbours", &K_));
+        OP_REQUIRES_OK(c, c->GetAttr("n_bins", &n_bins_));
+        OP_REQUIRES_OK(c, c->GetAttr("max_bin_dims", &max_bin_dims_));
+        OP_REQUIRES_OK(c, c->GetAttr("tf_compatible", &tf_compat_));
+        OP_REQUIRES_OK(c, c->GetAttr("use_direction", &use_direction_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &coords = ctx->input(0), &rs = ctx->input(1), &dir = ctx->input(2);
+        const int n_vert = coords.dim_size(0), n_coords = coords.dim_size(1), n_rs = rs.dim_size(0);
+        Tensor *idx, *dist, *sorting;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, K_}, &idx));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, K_}, &dist));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(2, {n_vert}, &sorting));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_binned_select_knn_ragged_workspace_bytes(
+                                                 n_vert, K_, n_coords, n_rs, n_bins_, max_bin_dims_)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_binned_select_knn_ragged(
+            coords.flat<float>().data(), rs.flat<int>().data(), use_direction_ ? dir.flat<int>().data() : nullptr,
+            idx->flat<int>().data(), dist->flat<float>().data(), sorting->flat<int>().data(), n_vert, K_,
+            n_coords, n_rs, n_bins_, max_bin_dims_, tf_compat_, use_direction_, ws.ptr, ws.bytes, StreamOf(ctx)),
+            "HgcBinnedSelectKnnRagged"));
+    }
+private:
+    int K_, n_bins_, max_bin_dims_;
+    bool tf_compat_, use_direction_;
+};
+
+// The collection step of RaggedGravNet / DistanceWeightedMessagePassing
+// (modules/GravNetLayersRagged.py:3195-3204, 3587-3600): output [N, 2F] = [mean - own | max - own] of
+// AccumulateKnn(distance_scale * distsq, features, indices) over the slots first_slot.. of the rows.
+class HgcGravnetCollectGpuOp : public OpKernel {
+public:
+    explicit HgcGravnetCollectGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("first_slot", &first_slot_));
+        OP_REQUIRES_OK(c, c->GetAttr("distance_scale", &scale_));
+        OP_REQUIRES_OK(c, c->GetAttr("subtract_self", &subtract_self_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &dist = ctx->input(0), &feat = ctx->input(1), &idx = ctx->input(2);
+        const int n_vert = feat.dim_size(0), F = feat.dim_size(1), ld = idx.dim_size(1);
+        OP_REQUIRES(ctx, dist.dim_size(0) == n_vert && idx.dim_size(0) == n_vert && dist.dim_size(1) == ld,
+                    errors::InvalidArgument("HgcGravnetCollect expects matching first dimensions and neighbour counts."));
+        Tensor *out, *maxidx;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, 2 * F}, &out));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, F}, &maxidx));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_gravnet_collect(
+            dist.flat<float>().data(), idx.flat<int>().data(), ld, first_slot_, ld - first_slot_,
+            feat.flat<float>().data(), out->flat<float>().data(), 2 * F, maxidx->flat<int>().data(), n_vert, F,
+            scale_, subtract_self_, nullptr, StreamOf(ctx)), "HgcGravnetCollect"));
+    }
+private:
+    int first_slot_;
+    float scale_;
+    bool subtract_self_;
+};
+
+// BuildAndAssignCondensatesBinned of modules/assign_condensate_op.py:210-310 (without keep_noise).
+// alpha_idx comes back [N] with -1 after the last condensate; the wrapper slices it with
+// n_condensates[-1], which TensorFlow reads on the host anyway.
+class HgcBuildAndAssignCondensatesGpuOp : public OpKernel {
+public:
+    explicit HgcBuildAndAssignCondensatesGpuOp(OpKernelConstruction *c) : OpKernel(c) {
+        OP_REQUIRES_OK(c, c->GetAttr("beta_threshold", &beta_threshold_));
+        OP_REQUIRES_OK(c, c->GetAttr("distance_threshold", &distance_threshold_));
+        OP_REQUIRES_OK(c, c->GetAttr("assign_by_max_beta", &assign_by_max_beta_));
+        OP_REQUIRES_OK(c, c->GetAttr("nbin_dims", &nbin_dims_));
+    }
+    void Compute(OpKernelContext *ctx) override {
+        const Tensor &cc = ctx->input(0), &betas = ctx->input(1), &dist = ctx->input(2), &mask = ctx->input(3),
+                     &rs = ctx->input(4);
+        const int n = cc.dim_size(0), dims = cc.dim_size(1), n_rs = rs.dim_size(0);
+        Tensor *assignment, *asso, *alpha, *is_cond, *ncond;
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n}, &assignment));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n}, &asso));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(2, {n}, &alpha));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(3, {n}, &is_cond));
+        OP_REQUIRES_OK(ctx, ctx->allocate_output(4, {n_rs}, &ncond));
+        Workspace ws;
+        OP_REQUIRES_OK(ctx, ws.Allocate(ctx, hgc_build_and_assign_condensates_workspace_bytes(n, dims, n_rs, nbin_dims_)));
+        OP_REQUIRES_OK(ctx, FromHgc(hgc_build_and_assign_condensates(
+            cc.flat<float>().data(), betas.flat<float>().data(), dist.flat<float>().data(),
+            mask.dim_size(0) == n ? mask.flat<int>().data() : nullptr, rs.flat<int>().data(),
+            assignment->flat<int>().data(), asso->flat<int>().data(), alpha->flat<int>().data(),
+            is_cond->flat<uint8>().data(), ncond->flat<int>().data(), nullptr, n, dims, n_rs, beta_threshold_,
+            distance_threshold_, assign_by_max_beta_, nbin_dims_, ws.ptr, ws.bytes, StreamOf(ctx)),
+            "HgcBuildAndAssignCondensates"));
+    }
+private:
+    float beta_threshold_, distance_threshold_;
+    bool assign_by_max_beta_;
+    int nbin_dims_;
+};
+
 }  // namespace
 
 // Op signatures: identical to the reference's *_module.cc files.
@@ -312,6 +414,21 @@ REGISTER_OP("BinnedAssignToCondensates").Attr("beta_threshold: float").Attr("ass
     .Input("no_condensation_mask_h: int32").Input("row_splits_h: int32")
     .Output("assigned_h: int32").Output("assigned: int32").Output("alpha_indices: int32")
     .Output("association: int32").Output("n_condensates: int32");
+// wrapper-level ops (no counterpart in the reference)
+REGISTER_OP("HgcBinnedSelectKnnRagged").Attr("n_neighbours: int").Attr("n_bins: int = 0").Attr("max_bin_dims: int = 3")
+    .Attr("tf_compatible: bool = false").Attr("use_direction: bool = false")
+    .Input("coords: float").Input("row_splits: int32").Input("direction: int32")
+    .Output("indices: int32").Output("distances: float32").Output("sorting: int32");
+REGISTER_OP("HgcGravnetCollect").Attr("first_slot: int = 0").Attr("distance_scale: float = 10.0")
+    .Attr("subtract_self: bool = true")
+    .Input("distancesq: float32").Input("features: float32").Input("indices: int32")
+    .Output("out_features: float32").Output("out_max_idxs: int32");
+REGISTER_OP("HgcBuildAndAssignCondensates").Attr("beta_threshold: float").Attr("distance_threshold: float = 1.0")
+    .Attr("assign_by_max_beta: bool = false").Attr("nbin_dims: int = 3")
+    .Input("ccoords: float32").Input("betas: float32").Input("dist: float32").Input("no_condensation_mask: int32")
+    .Input("row_splits: int32")
+    .Output("assignment: int32").Output("association: int32").Output("alpha_idx: int32").Output("is_cond: uint8")
+    .Output("n_condensates: int32");
 
 REGISTER_KERNEL_BUILDER(Name("BinByCoordinates").Device(DEVICE_GPU).HostMemory("nbins").HostMemory("bin_width"),
                         BinByCoordinatesGpuOp);
@@ -323,5 +440,8 @@ REGISTER_KERNEL_BUILDER(Name("SelectKnnGrad").Device(DEVICE_GPU), SelectKnnGradG
 REGISTER_KERNEL_BUILDER(Name("LocalDistance").Device(DEVICE_GPU), LocalDistanceGpuOp);
 REGISTER_KERNEL_BUILDER(Name("PushKnn").Device(DEVICE_GPU), PushKnnGpuOp);
 REGISTER_KERNEL_BUILDER(Name("BinnedAssignToCondensates").Device(DEVICE_GPU), BinnedAssignToCondensatesGpuOp);
+REGISTER_KERNEL_BUILDER(Name("HgcBinnedSelectKnnRagged").Device(DEVICE_GPU), HgcBinnedSelectKnnRaggedGpuOp);
+REGISTER_KERNEL_BUILDER(Name("HgcGravnetCollect").Device(DEVICE_GPU), HgcGravnetCollectGpuOp);
+REGISTER_KERNEL_BUILDER(Name("HgcBuildAndAssignCondensates").Device(DEVICE_GPU), HgcBuildAndAssignCondensatesGpuOp);
 
 }  // namespace tensorflow
