@@ -6,11 +6,12 @@
 // its radius, repeat.  The same result is produced here in three parallel steps:
 //   1. priority sort  : the high-beta hits of each event are ordered by (beta descending, position
 //                       ascending) with the stable counting sort of radix_sort.cu;
-//   2. claim pass     : one block per event walks that order in windows of 1024 hits; a window is
-//                       first tested against all condensates confirmed so far (parallel), then the
-//                       survivors are resolved in order, each new condensate claiming the later
-//                       survivors it covers.  A hit is a condensate exactly when no earlier
-//                       condensate covers it, which is the greedy rule;
+//   2. claim pass     : a cluster of 8 blocks per event walks that order in windows of 8192 hits;
+//                       a window is first tested against all condensates confirmed so far
+//                       (parallel), then the survivors are settled in order, 32 at a time, each
+//                       new condensate closing the later survivors it covers.  A hit is a
+//                       condensate exactly when no earlier condensate covers it, which is the
+//                       greedy rule;
 //   3. assignment     : every hit of the event is tested against the event's condensates in rank
 //                       order (tiles of the list in shared memory): the first that covers it wins
 //                       (assign_by_max_beta) or the reference's distance fold is applied.
@@ -96,141 +97,223 @@ __device__ __forceinline__ float centre_distsq(const float *c, const float *x, i
 // Step 2.  order[] lists, per event, the subset positions in priority order.
 //
 // A cluster of kClusterBlocks blocks works on one event and walks the priority order in windows of
-// kWindow hits.  (a) Every block tests its 1024 hits of the window against the condensates confirmed
-// in earlier windows and leaves a flag per hit.  (b) After a cluster barrier, block 0 resolves the
-// survivors in order: the first open hit becomes the next condensate and closes the later survivors
-// it covers.  (c) A second cluster barrier publishes the longer condensate list to all blocks.
-// The barriers are the hardware cluster barrier; every block of a cluster runs the same number of
-// windows, so none can be left waiting.
+// kWindow hits, one hit per thread.
+//  (a) Every thread tests its hit against the condensates confirmed in earlier windows.
+//  (b) The hits still open are settled in batches of the first 32 open ones, in priority order: a
+//      prefix sum over the cluster ranks the open hits; the batch goes through a small staging
+//      area in global memory to every block; warp i of every block tests batch hit i against the
+//      later hits of the batch and every thread then walks the batch in order -- a hit not covered
+//      by an earlier condensate of the batch becomes a condensate.  Every thread drops its own hit
+//      if one of the new condensates covers it.  (All open hits before a batch member are batch
+//      members too, so a new condensate only ever meets later hits, as in the sequential loop.)
+// All blocks take the same decisions from the same data, so only the condensate lists that later
+// kernels read are published (by block 0).  The barriers are the hardware cluster barrier; every
+// block of a cluster runs the same number of windows and batches, so none can be left waiting.
+//
+// A condensate is held as NR float4: its coordinates and, in the last slot, its squared radius (-1
+// for a masked condensate, which covers nothing but itself): NR = 1 up to 3 dimensions, 2 up to 7,
+// 3 for 8.
 constexpr int kClusterBlocks = 8;
 constexpr int kWindow = kClusterBlocks * kClaimThreads;
-constexpr int kItems = kWindow / kClaimThreads;  // survivors a thread of block 0 looks after
+constexpr int kBatch = 32;
+constexpr int kStageInts = 8 + kBatch * (3 * 4 + 2);  // block counts, batch records, positions, flags
 
-__device__ __forceinline__ bool covers(const float *c, float r2, int lonely, int c_pos, const float *x, int dims,
-                                       int x_pos, int x_mask)
+template <int NR> struct Rec { float v[NR * 4]; };
+template <int NR> __host__ __device__ constexpr int rec_dims() { return NR == 3 ? 8 : NR * 4 - 1; }
+template <int NR> __host__ __device__ constexpr int rec_r2_slot() { return NR == 3 ? 8 : NR * 4 - 1; }
+
+template <int NR>
+__device__ __forceinline__ Rec<NR> load_rec_shared(const float4 *p)
 {
-    if (lonely) return c_pos == x_pos;
-    return x_mask == 0 && centre_distsq(c, x, dims) <= r2;
+    Rec<NR> r;
+#pragma unroll
+    for (int u = 0; u < NR; u++) {
+        const float4 q = p[u];
+        r.v[4 * u] = q.x; r.v[4 * u + 1] = q.y; r.v[4 * u + 2] = q.z; r.v[4 * u + 3] = q.w;
+    }
+    return r;
 }
 
+// Squared distance over the first `dims` slots, rounded like centre_distsq.
+template <int NR>
+__device__ __forceinline__ float rec_distsq(const Rec<NR> &c, const Rec<NR> &x, int dims)
+{
+    float s = 0.f;
+#pragma unroll
+    for (int d = 0; d < rec_dims<NR>(); d++)
+        if (d < dims) {
+            const float t = __fsub_rn(c.v[d], x.v[d]);
+            s = __fadd_rn(s, __fmul_rn(t, t));
+        }
+    return s;
+}
+
+template <int NR>
 __global__ void __cluster_dims__(kClusterBlocks, 1, 1) __launch_bounds__(kClaimThreads)
 claim_kernel(int dims, const float *__restrict__ ccoords_h, const float *__restrict__ dist_h,
              const int *__restrict__ mask_h, const int *__restrict__ original_indices_h,
              const int *__restrict__ row_splits_h, const int *__restrict__ order,
-             int *__restrict__ status_h, int *__restrict__ alpha_indices, int *__restrict__ open_flags,
+             int *__restrict__ status_h, int *__restrict__ alpha_indices, int *__restrict__ stage_all,
              CondList cl)
 {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ float s_c[kCondTile][kMaxDims];
-    __shared__ float s_r2[kCondTile];
-    __shared__ int s_pos[kCondTile];
-    __shared__ int s_lonely[kCondTile];
-    __shared__ int s_first[32];
-    __shared__ float s_new_c[kMaxDims];
-    __shared__ float s_new_r2;
-    __shared__ int s_new_pos, s_new_lonely;
+    __shared__ float4 s_rec[kCondTile][NR];
+    __shared__ float4 s_b[kBatch][NR];
+    __shared__ int s_b_pos[kBatch], s_b_flags[kBatch];  // flags: bit 0 = masked condensate, bit 1 = mask != 0
+    __shared__ unsigned s_cov[kBatch];
+    __shared__ int s_wcnt[32];
 
     const int rank = (int)cluster.block_rank();
     const int e = blockIdx.x / kClusterBlocks;
     const int off = row_splits_h[e], n_h = row_splits_h[e + 1] - off;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    int *flags = open_flags + (size_t)e * kWindow;
-    volatile int *count = cl.count + e;
+    int *stage_counts = stage_all + (size_t)e * kStageInts;
+    float *stage_rec = reinterpret_cast<float *>(stage_counts + 8);
+    int *stage_pos = stage_counts + 8 + kBatch * 12;
+    int *stage_flags = stage_pos + kBatch;
+    int n_cond = 0;
 
     for (int w0 = 0; w0 < n_h; w0 += kWindow) {
-        int n_cond = *count;  // published by block 0 before the barrier that ended the previous window
-
-        // (a) this block's hits of the window against the confirmed condensates
         const int p = w0 + rank * kClaimThreads + t;
         const bool active = p < n_h;
         int a = 0, my_mask = 0;
-        float x[kMaxDims];
+        Rec<NR> x;
+#pragma unroll
+        for (int d = 0; d < NR * 4; d++) x.v[d] = 0.f;
         if (active) {
             a = order[off + p];
             my_mask = mask_h[a];
 #pragma unroll
-            for (int d = 0; d < kMaxDims; d++) x[d] = d < dims ? ccoords_h[(size_t)a * dims + d] : 0.f;
+            for (int d = 0; d < rec_dims<NR>(); d++)
+                if (d < dims) x.v[d] = ccoords_h[(size_t)a * dims + d];
+            const float radius = dist_h[a];
+            x.v[rec_r2_slot<NR>()] = __fmul_rn(radius, radius);
         }
         bool open = active;
+
+        // (a) against the condensates of earlier windows (written by block 0 on another SM during
+        // this launch: read past the incoherent L1)
         for (int c0 = 0; c0 < n_cond; c0 += kCondTile) {
             const int nt = min(kCondTile, n_cond - c0);
             __syncthreads();
             if (t < nt) {
-                // written by block 0 on another SM during this launch: read past the (incoherent) L1
-                for (int d = 0; d < dims; d++) s_c[t][d] = __ldcg(cl.centre + (size_t)(off + c0 + t) * dims + d);
-                s_r2[t] = __ldcg(cl.radius_sq + off + c0 + t);
-                s_pos[t] = __ldcg(cl.subset_pos + off + c0 + t);
-                s_lonely[t] = __ldcg(cl.lonely + off + c0 + t);
+                Rec<NR> r;
+#pragma unroll
+                for (int d = 0; d < NR * 4; d++) r.v[d] = 0.f;
+#pragma unroll
+                for (int d = 0; d < rec_dims<NR>(); d++)
+                    if (d < dims) r.v[d] = __ldcg(cl.centre + (size_t)(off + c0 + t) * dims + d);
+                r.v[rec_r2_slot<NR>()] = __ldcg(cl.lonely + off + c0 + t) ? -1.f : __ldcg(cl.radius_sq + off + c0 + t);
+#pragma unroll
+                for (int u = 0; u < NR; u++)
+                    s_rec[t][u] = make_float4(r.v[4 * u], r.v[4 * u + 1], r.v[4 * u + 2], r.v[4 * u + 3]);
             }
             __syncthreads();
-            if (open) {
-                for (int c = 0; c < nt; c++)
-                    if (covers(s_c[c], s_r2[c], s_lonely[c], s_pos[c], x, dims, a, my_mask)) { open = false; break; }
+            if (open && my_mask == 0) {
+                for (int c = 0; c < nt; c++) {
+                    const Rec<NR> r = load_rec_shared<NR>(s_rec[c]);
+                    if (rec_distsq<NR>(r, x, dims) <= r.v[rec_r2_slot<NR>()]) { open = false; break; }
+                }
             }
         }
-        __stcg(flags + rank * kClaimThreads + t, open ? 1 : 0);
-        __threadfence();
-        cluster.sync();
 
-        // (b) block 0: the survivors of the whole window, in priority order
-        if (rank == 0) {
-            unsigned open_bits = 0u;
+        // (b) batches of the first kBatch open hits
+        for (int guard = 0; guard <= kWindow; guard++) {
+            const unsigned bal = __ballot_sync(0xffffffffu, open);
+            // (the shared arrays of the previous round were last read before that round's cluster barriers)
+            if (lane == 0) s_wcnt[warp] = __popc(bal);
+            __syncthreads();
+            const int wv = s_wcnt[lane];
+            int wincl = wv;
 #pragma unroll
-            for (int q = 0; q < kItems; q++)
-                if (__ldcg(flags + t * kItems + q)) open_bits |= 1u << q;
-            for (int guard = 0; guard <= kWindow; guard++) {
-                int first = open_bits ? t * kItems + __ffs(open_bits) - 1 : kWindow;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, wincl, o);
+                if (lane >= o) wincl += v;
+            }
+            const int warp_base = __shfl_sync(0xffffffffu, wincl - wv, warp);
+            const int blk_total = __shfl_sync(0xffffffffu, wincl, 31);
+            if (t == 0) __stcg(stage_counts + rank, blk_total);
+            __threadfence();
+            cluster.sync();
+            int cv = lane < kClusterBlocks ? __ldcg(stage_counts + lane) : 0;
+            int cincl = cv;
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
-                __syncthreads();
-                if (lane == 0) s_first[warp] = first;
-                __syncthreads();
-                first = s_first[lane];
+            for (int o = 1; o < kClusterBlocks; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, cincl, o);
+                if (lane >= o) cincl += v;
+            }
+            const int total = __shfl_sync(0xffffffffu, cincl, kClusterBlocks - 1);
+            if (total == 0) break;  // the same in every block of the cluster
+            const int blk_base = __shfl_sync(0xffffffffu, cincl - cv, rank);
+            const int m = min(total, kBatch);
+            const int my_r = blk_base + warp_base + __popc(bal & ((1u << lane) - 1u));
+            if (open && my_r < kBatch) {
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
-                if (first >= kWindow) break;
-                if (first / kItems == t) {
-                    const int pos = order[off + w0 + first];
-                    const float radius = dist_h[pos];
-                    const int lonely = mask_h[pos] > 0;
-                    for (int d = 0; d < dims; d++) {
-                        const float v = ccoords_h[(size_t)pos * dims + d];
-                        s_new_c[d] = v;
-                        cl.centre[(size_t)(off + n_cond) * dims + d] = v;
-                    }
-                    s_new_r2 = __fmul_rn(radius, radius);
-                    s_new_pos = pos;
-                    s_new_lonely = lonely;
-                    cl.radius_sq[off + n_cond] = __fmul_rn(radius, radius);
-                    cl.subset_pos[off + n_cond] = pos;
-                    cl.lonely[off + n_cond] = lonely;
-                    status_h[pos] = 1;
-                    alpha_indices[off + n_cond] = original_indices_h[pos];
-                    open_bits &= ~(1u << (first - t * kItems));
-                }
-                __syncthreads();
-                unsigned todo = open_bits;
-                while (todo) {
-                    const int q = __ffs(todo) - 1;
-                    todo &= todo - 1;
-                    if (t * kItems + q < first) continue;
-                    const int pos = order[off + w0 + t * kItems + q];
-                    float y[kMaxDims];
+                for (int d = 0; d < NR * 4; d++) __stcg(stage_rec + my_r * 12 + d, x.v[d]);
+                __stcg(stage_pos + my_r, a);
+                __stcg(stage_flags + my_r, (my_mask > 0 ? 1 : 0) | (my_mask != 0 ? 2 : 0));
+            }
+            __threadfence();
+            cluster.sync();
+            if (t < m) {
+                float v[NR * 4];
 #pragma unroll
-                    for (int d = 0; d < kMaxDims; d++) y[d] = d < dims ? ccoords_h[(size_t)pos * dims + d] : 0.f;
-                    if (covers(s_new_c, s_new_r2, s_new_lonely, s_new_pos, y, dims, pos, mask_h[pos]))
-                        open_bits &= ~(1u << q);
-                }
-                n_cond++;
+                for (int d = 0; d < NR * 4; d++) v[d] = __ldcg(stage_rec + t * 12 + d);
+#pragma unroll
+                for (int u = 0; u < NR; u++) s_b[t][u] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+                s_b_pos[t] = __ldcg(stage_pos + t);
+                s_b_flags[t] = __ldcg(stage_flags + t);
             }
             __syncthreads();
-            if (t == 0) *count = n_cond;
-            __threadfence();
+            if (warp < m) {
+                bool cov = false;
+                if (lane < m && lane > warp && !(s_b_flags[warp] & 1) && !(s_b_flags[lane] & 2)) {
+                    const Rec<NR> ci = load_rec_shared<NR>(s_b[warp]);
+                    const Rec<NR> cj = load_rec_shared<NR>(s_b[lane]);
+                    cov = rec_distsq<NR>(ci, cj, dims) <= ci.v[rec_r2_slot<NR>()];
+                }
+                const unsigned cm = __ballot_sync(0xffffffffu, cov);
+                if (lane == 0) s_cov[warp] = cm;
+            }
+            __syncthreads();
+            unsigned cond = 0u, dead = 0u;
+            for (int i = 0; i < m; i++)
+                if (!((dead >> i) & 1u)) {
+                    cond |= 1u << i;
+                    dead |= s_cov[i];
+                }
+            if (rank == 0 && warp == 0 && ((cond >> lane) & 1u)) {  // publish the new condensates, in order
+                const int slot = off + n_cond + __popc(cond & ((1u << lane) - 1u));
+                const int pos = s_b_pos[lane];
+                const Rec<NR> c = load_rec_shared<NR>(s_b[lane]);
+#pragma unroll
+                for (int d = 0; d < rec_dims<NR>(); d++)
+                    if (d < dims) cl.centre[(size_t)slot * dims + d] = c.v[d];
+                cl.radius_sq[slot] = c.v[rec_r2_slot<NR>()];
+                cl.subset_pos[slot] = pos;
+                cl.lonely[slot] = s_b_flags[lane] & 1;
+                status_h[pos] = 1;
+                alpha_indices[slot] = original_indices_h[pos];
+            }
+            if (open) {
+                if (my_r < kBatch) {
+                    open = false;  // a batch member is a new condensate or covered by one
+                } else if (my_mask == 0) {
+                    for (unsigned cm = cond; cm; cm &= cm - 1u) {
+                        const int i = __ffs(cm) - 1;
+                        if (s_b_flags[i] & 1) continue;  // a masked condensate covers nothing but itself
+                        const Rec<NR> c = load_rec_shared<NR>(s_b[i]);
+                        if (rec_distsq<NR>(c, x, dims) <= c.v[rec_r2_slot<NR>()]) { open = false; break; }
+                    }
+                }
+            }
+            n_cond += __popc(cond);
         }
-        // (c) the longer list becomes visible to all blocks of the cluster
-        cluster.sync();
+        // the lists block 0 wrote become visible to the other blocks with the fence and the cluster
+        // barrier that end every round of (b), the last one included
     }
+    if (rank == 0 && t == 0) cl.count[e] = n_cond;
 }
 
 __global__ void condensate_totals_kernel(const int *__restrict__ count, int num_rows,
@@ -335,7 +418,7 @@ using namespace hgc;
 
 namespace {
 struct CondBuffers {
-    int *beta_keys, *event_keys, *k1, *v1, *k2, *v2, *tk, *tv, *hist, *open_flags;
+    int *beta_keys, *event_keys, *k1, *v1, *k2, *v2, *tk, *tv, *hist, *stage;
     CondList cl;
 };
 template <typename W>
@@ -354,7 +437,7 @@ void cond_layout(W &ws, int n_h, int num_rows, int dims, CondBuffers *out)
     b.cl.subset_pos = ws.template take<int>(n);
     b.cl.lonely = ws.template take<int>(n);
     b.cl.count = ws.template take<int>(num_rows > 0 ? num_rows : 0);
-    b.open_flags = ws.template take<int>((size_t)(num_rows > 0 ? num_rows : 0) * kWindow);
+    b.stage = ws.template take<int>((size_t)(num_rows > 0 ? num_rows : 0) * kStageInts);
     if (out) *out = b;
 }
 struct CondSizer {
@@ -420,9 +503,14 @@ extern "C" int hgc_binned_assign_to_condensates(
         gather_int_kernel<<<div_up(n_vert_h, 256), 256, 0, stream>>>(b.event_keys, b.v1, b.k1, n_vert_h);
         HGC_LAUNCH_CHECK();
         if (int rc = sort_pairs(b.k1, b.v1, b.k2, b.v2, b.tk, b.tv, b.hist, n_vert_h, bits_for(num_rows), stream)) return rc;
-        claim_kernel<<<num_rows * kClusterBlocks, kClaimThreads, 0, stream>>>(
-                dimensions, d_ccoords_h, d_dist_h, d_no_condensation_mask_h, d_original_indices_h, d_row_splits_h,
-                b.v2, d_high_assigned_status_h, d_alpha_indices, b.open_flags, b.cl);
+#define HGC_CLAIM(NR)                                                                                       \
+    claim_kernel<NR><<<num_rows * kClusterBlocks, kClaimThreads, 0, stream>>>(                                \
+            dimensions, d_ccoords_h, d_dist_h, d_no_condensation_mask_h, d_original_indices_h, d_row_splits_h, \
+            b.v2, d_high_assigned_status_h, d_alpha_indices, b.stage, b.cl)
+        if (dimensions <= 3) HGC_CLAIM(1);
+        else if (dimensions <= 7) HGC_CLAIM(2);
+        else HGC_CLAIM(3);
+#undef HGC_CLAIM
         HGC_LAUNCH_CHECK();
     }
     condensate_totals_kernel<<<1, 32, 0, stream>>>(b.cl.count, num_rows, d_n_condensates);
