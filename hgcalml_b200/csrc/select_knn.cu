@@ -8,7 +8,7 @@ namespace {
 
 #ifdef HGC_KNN_STATS
 // work counters of the search kernel (instrumented builds only: make EXTRA=-DHGC_KNN_STATS)
-__device__ unsigned long long g_knn_stats[16];
+__device__ unsigned long long g_knn_stats[96];
 #endif
 
 // [n_vert, n_coords] floats (optionally gathered through perm) -> zero-padded float4 records
@@ -113,12 +113,14 @@ using namespace hgc;
 #ifdef HGC_KNN_STATS
 // Tuning aid: copies the search kernel's work counters (queries, candidates offered, accepted,
 // list merges, boxes tested, chunks scanned, steps, then cycles: per query, in merges, in candidate
-// steps; filled only by a build with -DHGC_KNN_STATS) to the host and clears them.
-extern "C" int hgc_debug_knn_stats(unsigned long long *out16)
+// steps, ...; from [16] on, per final shell 0..7: queries, candidates, cycles, accepted, cycles in merges /
+// candidate steps / enumeration / box tests, steps, boxes; filled only by
+// a build with -DHGC_KNN_STATS) to the host and clears them.
+extern "C" int hgc_debug_knn_stats(unsigned long long *out96)
 {
     HGC_CUDA_TRY(cudaDeviceSynchronize());
-    HGC_CUDA_TRY(cudaMemcpyFromSymbol(out16, g_knn_stats, sizeof(unsigned long long) * 16));
-    unsigned long long zero[16] = {0};
+    HGC_CUDA_TRY(cudaMemcpyFromSymbol(out96, g_knn_stats, sizeof(unsigned long long) * 96));
+    unsigned long long zero[96] = {0};
     HGC_CUDA_TRY(cudaMemcpyToSymbol(g_knn_stats, zero, sizeof(zero)));
     return HGC_OK;
 }

@@ -14,6 +14,8 @@
 //    the same unfused subtract/multiply/add sequence as the point distance, rounding is monotone,
 //    so no point of the chunk can have a smaller computed distance than the box.
 //  * Short ranges (sparse regions) are laid end to end and walked 32 candidates at a time.
+//  * From the second shell on, bins whose distance to the query's bin already puts them beyond the
+//    K-th best are left out of the ranges (the shells are cubes, the K-th best cuts a ball).
 //
 // The best K-1 candidates live in registers as a sorted list striped over the lanes (rank r in
 // register r/32 of lane r%32), keyed by (distance bits, index) in one 64-bit word so that ties
@@ -41,6 +43,12 @@ typedef double knn_key;
 #endif
 #ifndef HGC_KNN_FLUSH_AT
 #define HGC_KNN_FLUSH_AT 32
+#endif
+#ifndef HGC_KNN_BINPRUNE
+#define HGC_KNN_BINPRUNE 1
+#endif
+#ifndef HGC_KNN_OFFER2
+#define HGC_KNN_OFFER2 1
 #endif
 #ifndef HGC_KNN_MIN_BLOCKS
 #define HGC_KNN_MIN_BLOCKS 4
@@ -249,12 +257,26 @@ struct Query {
         offer_inner(valid, j);
         HGC_STAT(t_offer += (clock64() - t0) - (t_flush - f0));
     }
+    // Two candidates per lane: both coordinate loads are issued before either is used, so their
+    // latencies overlap (candidates of sparse regions come from many short ranges and miss L1).
+    __device__ __forceinline__ void offer2(bool valid0, int j0, bool valid1, int j1)
+    {
+        HGC_STAT(const long long t0 = clock64(); const long long f0 = t_flush);
+        const Point<NV4> p0 = load_point<NV4>(pts, (size_t)(valid0 ? j0 : self));
+        const Point<NV4> p1 = load_point<NV4>(pts, (size_t)(valid1 ? j1 : self));
+        offer_loaded(valid0, j0, p0);
+        if (__any_sync(0xffffffffu, valid1)) offer_loaded(valid1, j1, p1);
+        HGC_STAT(t_offer += (clock64() - t0) - (t_flush - f0));
+    }
     __device__ __forceinline__ void offer_inner(bool valid, int j)
+    {
+        offer_loaded(valid, j, load_point<NV4>(pts, (size_t)(valid ? j : self)));
+    }
+    __device__ __forceinline__ void offer_loaded(bool valid, int j, const Point<NV4> &p)
     {
         bool pass = false;
         knn_key key = HGC_KNN_INF_KEY;
         if (valid) {
-            const Point<NV4> p = load_point<NV4>(pts, (size_t)j);
             const float ds = distsq<NV4>(q, p);
             key = make_key(ds, j);
             pass = j != self && key < thr;
@@ -316,7 +338,7 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
         Q.thr = HGC_KNN_INF_KEY;
         Q.buffered = 0;
         HGC_STAT(Q.n_offered = Q.n_accepted = Q.n_flushes = Q.n_steps = 0; Q.t_flush = Q.t_offer = 0; const long long t_query0 = clock64());
-        HGC_STAT(unsigned st_boxes = 0; unsigned st_chunks = 0; long long t_enum = 0; long long t_box = 0; long long t_out = 0);
+        HGC_STAT(int st_dfinal = 0; unsigned st_boxes = 0; unsigned st_chunks = 0; long long t_enum = 0; long long t_box = 0; long long t_out = 0);
         Q.lane = lane;
         Q.self = i;
         Q.buf = s_buf[warp];
@@ -341,6 +363,7 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
             // Shells 0 and 1 are always both scanned (the stop rule cannot fire at d = 0), so the
             // first pass covers the whole 3^CB cube; later passes cover one shell each.
             for (int d = 1;; d++) {
+                HGC_STAT(st_dfinal = d);
                 // in-grid extent of the shell's bounding cube in the leading CB-1 dimensions
                 int lo[CB], span[CB], cells = 1, centre = 0;
                 float inv_span[CB];
@@ -368,6 +391,7 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
                         int c = (slot >> 1) + centre, flat = 0;
                         if (c >= cells) c -= cells;
                         bool surface = d == 1;
+                        float lead_lb = 0.f;  // lower bound of the squared distance from the leading dimensions
 #pragma unroll
                         for (int k = CB - 2; k >= 0; k--) {
                             int quot;
@@ -382,6 +406,8 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
                             flat += g * stride[k];
                             const int off = g - qb[k];
                             surface = surface || off == d || off == -d;
+                            const float gap = fmaxf((float)abs(off) - 1.01f, 0.f) * bw;
+                            lead_lb += gap * gap;
                         }
                         int b0 = -1, b1 = -1;
                         if (surface) {
@@ -392,11 +418,29 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
                             if (last_hi < nb[CB - 1]) b0 = b1 = last_hi;
                         }
                         if (b0 >= 0 && b0 <= b1) {
-                            const int g0 = event_offset + flat + b0, g1 = event_offset + flat + b1;
+                            const int g1 = event_offset + flat + b1;
                             if (g1 < a.n_bboundaries - 1) {
                                 slot_in_grid = true;
-                                start = a.bin_boundaries[g0];
-                                len = a.bin_boundaries[g1 + 1] - start;
+                                // Beyond the first pass, bins that cannot hold anything closer than the
+                                // K-th best are left out.  A hit whose bin is |o| bins from the query's
+                                // in one dimension is more than (|o| - 1) bin widths away in it (the
+                                // 0.01 bins and the factor on the K-th best absorb the rounding of the
+                                // bin arithmetic and of the distances); along the last dimension the
+                                // row is cut to the bins the remaining room allows.
+                                if (HGC_KNN_BINPRUNE && d >= 2 && Q.thr != HGC_KNN_INF_KEY) {
+                                    const float room = Q.kth() * 1.00001f - lead_lb;
+                                    if (room < 0.f) {
+                                        b1 = b0 - 1;
+                                    } else if (room < 1e30f) {
+                                        const int omax = (int)(sqrtf(room) / bw + 1.02f);
+                                        b0 = max(b0, qb[CB - 1] - omax);
+                                        b1 = min(b1, qb[CB - 1] + omax);
+                                    }
+                                }
+                                if (b0 <= b1) {
+                                    start = a.bin_boundaries[event_offset + flat + b0];
+                                    len = a.bin_boundaries[event_offset + flat + b1 + 1] - start;
+                                }
                             } else {
                                 flag_status(a.status, HGC_STATUS_FLAT_BIN_OVERFLOW);
                             }
@@ -472,14 +516,18 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
                     s_end[warp][lane] = incl;
                     __syncwarp();
                     int r = 0;
-                    for (int t0 = 0; t0 < total; t0 += kWarp) {
-                        const int v = t0 + lane;
-                        int j = 0;
-                        if (v < total) {
-                            while (v >= s_end[warp][r]) r++;
-                            j = s_start[warp][r] + v;
+                    for (int t0 = 0; t0 < total; t0 += (HGC_KNN_OFFER2 ? 2 : 1) * kWarp) {
+                        const int v0 = t0 + lane, v1 = HGC_KNN_OFFER2 ? t0 + kWarp + lane : total;
+                        int j0 = 0, j1 = 0;
+                        if (v0 < total) {
+                            while (v0 >= s_end[warp][r]) r++;
+                            j0 = s_start[warp][r] + v0;
                         }
-                        Q.offer(v < total, j);
+                        if (v1 < total) {
+                            while (v1 >= s_end[warp][r]) r++;
+                            j1 = s_start[warp][r] + v1;
+                        }
+                        Q.offer2(v0 < total, j0, v1 < total, j1);
                     }
                 }
 
@@ -531,6 +579,19 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
             atomicAdd(&a.stats[10], (unsigned long long)t_enum);
             atomicAdd(&a.stats[11], (unsigned long long)t_box);
             atomicAdd(&a.stats[12], (unsigned long long)t_out);
+            {   // by the shell the search ended in (1..7, 7 = seven or more): queries, candidates, cycles
+                const int db = st_dfinal < 7 ? st_dfinal : 7;
+                atomicAdd(&a.stats[16 + db], 1ull);
+                atomicAdd(&a.stats[24 + db], (unsigned long long)Q.n_offered);
+                atomicAdd(&a.stats[32 + db], (unsigned long long)(to0 - t_query0));
+                atomicAdd(&a.stats[40 + db], (unsigned long long)Q.n_accepted);
+                atomicAdd(&a.stats[48 + db], (unsigned long long)Q.t_flush);
+                atomicAdd(&a.stats[56 + db], (unsigned long long)Q.t_offer);
+                atomicAdd(&a.stats[64 + db], (unsigned long long)t_enum);
+                atomicAdd(&a.stats[72 + db], (unsigned long long)t_box);
+                atomicAdd(&a.stats[80 + db], (unsigned long long)Q.n_steps);
+                atomicAdd(&a.stats[88 + db], (unsigned long long)st_boxes);
+            }
         }
 #endif
     }
