@@ -13,8 +13,20 @@
 namespace hgc {
 namespace {
 
-constexpr int kAccThreads = 256;
-constexpr int kAccTile = 512;  // consecutive hits a block processes before it jumps to its next tile
+#ifndef HGC_ACC_CH16
+#define HGC_ACC_CH16 4
+#endif
+#ifndef HGC_ACC_MINB16
+#define HGC_ACC_MINB16 5
+#endif
+#ifndef HGC_ACC_THREADS
+#define HGC_ACC_THREADS 256
+#endif
+#ifndef HGC_ACC_TILE
+#define HGC_ACC_TILE 256
+#endif
+constexpr int kAccThreads = HGC_ACC_THREADS;
+constexpr int kAccTile = HGC_ACC_TILE;  // consecutive hits a block processes before it jumps to its next tile
 
 // Packed float32x2 arithmetic (two independent, individually rounded float32 operations per
 // instruction on sm_100): same results as scalar __fmul_rn / __fadd_rn, half the issue slots.
@@ -36,7 +48,7 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b)
 }
 
 template <int LPH, int VPL, int CH, int MINB, bool EXP, bool WITH_ARG>
-__global__ void __launch_bounds__(kAccThreads, MINB)
+__global__ void __launch_bounds__(kAccThreads, (MINB * 256 / kAccThreads) > 0 ? (MINB * 256 / kAccThreads) : 1)
 accumulate_vec_kernel(const float *__restrict__ weights, const float4 *__restrict__ feat,
                       const int *__restrict__ idxs, float *__restrict__ out, int *__restrict__ out_arg,
                       int n_vert, int K, int ldk, int F4, int n_out_feat, bool mean_and_max,
@@ -280,9 +292,9 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
 #define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, ldk, F4, n_out, mm, order, scale, sub_self, stream)
     if (F4 <= 4) HGC_VEC(4, 1, 4, 3);
     if (F4 <= 8) HGC_VEC(8, 1, 4, 3);
-    // F = 64: 16 lanes per hit, 4 rows in flight, 64 registers (4 blocks per SM) measured best of
-    // {8 rows / 2 blocks, 4 / 3, 4 / 4, 2 / 4, 8 / 3}
-    if (F4 <= 16) HGC_VEC(16, 1, 4, 4);
+    // F = 64: 16 lanes per hit, 4 rows in flight, 5 blocks per SM (51 registers) measured best of
+    // {rows in flight / blocks per SM: 8/2, 8/3, 4/3, 4/4, 4/5, 2/4, 2/5, 2/6}; tiles of 256 hits best of 64..2048
+    if (F4 <= 16) HGC_VEC(16, 1, HGC_ACC_CH16, HGC_ACC_MINB16);
     if (F4 <= 32) HGC_VEC(32, 1, 4, 3);
     if (F4 <= 64) HGC_VEC(32, 2, 4, 2);
     HGC_VEC(32, 4, 2, 1);

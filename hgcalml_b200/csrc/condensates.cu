@@ -82,18 +82,6 @@ __global__ void init_outputs_kernel(int *__restrict__ status_h, int *__restrict_
     if (i < n) { assignment[i] = -1; association[i] = -1; }
 }
 
-__device__ __forceinline__ float centre_distsq(const float *c, const float *x, int dims)
-{
-    float s = 0.f;
-#pragma unroll
-    for (int d = 0; d < kMaxDims; d++)
-        if (d < dims) {
-            const float t = __fsub_rn(c[d], x[d]);
-            s = __fadd_rn(s, __fmul_rn(t, t));
-        }
-    return s;
-}
-
 // Step 2.  order[] lists, per event, the subset positions in priority order.
 //
 // A cluster of kClusterBlocks blocks works on one event and walks the priority order in windows of
@@ -134,7 +122,8 @@ __device__ __forceinline__ Rec<NR> load_rec_shared(const float4 *p)
     return r;
 }
 
-// Squared distance over the first `dims` slots, rounded like centre_distsq.
+// Squared distance over the first `dims` slots: subtract, multiply, add, each rounded on its own, in
+// coordinate order (the reference's loop, binned_assign_to_condensates_kernel.cc:88-91,103-106).
 template <int NR>
 __device__ __forceinline__ float rec_distsq(const Rec<NR> &c, const Rec<NR> &x, int dims)
 {
@@ -326,7 +315,11 @@ __global__ void condensate_totals_kernel(const int *__restrict__ count, int num_
     }
 }
 
-// Step 3.  A block covers 256 consecutive hits, which may straddle events.
+// Step 3.  A block covers 256 consecutive hits, which may straddle events.  Condensates are staged in
+// shared memory as in the claim pass (NR float4 each: coordinates and squared radius, -1 for a masked
+// condensate).  A hit with a non-zero mask is covered by nothing but itself (if it is a masked
+// condensate); those few hits look for their own entry in the position list instead.
+template <int NR>
 __global__ void __launch_bounds__(kAssignThreads)
 assign_kernel(int dims, const float *__restrict__ ccoords, const int *__restrict__ mask,
               const int *__restrict__ indices_to_filtered, const int *__restrict__ original_indices_h,
@@ -334,18 +327,20 @@ assign_kernel(int dims, const float *__restrict__ ccoords, const int *__restrict
               int n_vert, bool by_max_beta, CondList cl, int *__restrict__ assignment,
               int *__restrict__ association)
 {
-    __shared__ float s_c[kCondTile][kMaxDims];
-    __shared__ float s_r2[kCondTile];
+    __shared__ float4 s_rec[kCondTile][NR];
     __shared__ int s_pos[kCondTile];
     __shared__ int s_lonely[kCondTile];
 
     const int v = blockIdx.x * kAssignThreads + threadIdx.x;
     const bool live = v < n_vert;
-    float x[kMaxDims];
+    Rec<NR> x;
+#pragma unroll
+    for (int d = 0; d < NR * 4; d++) x.v[d] = 0.f;
     int my_mask = 0, my_filtered = -1;
     if (live) {
 #pragma unroll
-        for (int d = 0; d < kMaxDims; d++) x[d] = d < dims ? ccoords[(size_t)v * dims + d] : 0.f;
+        for (int d = 0; d < rec_dims<NR>(); d++)
+            if (d < dims) x.v[d] = ccoords[(size_t)v * dims + d];
         my_mask = mask[v];
         my_filtered = indices_to_filtered[v];
     }
@@ -361,7 +356,7 @@ assign_kernel(int dims, const float *__restrict__ ccoords, const int *__restrict
         }
         e = lo - 1;
     }
-    int best = -1, best_pos = -1;
+    int best = -1, best_off = 0;
     float min_distance = 10e20f;
 
     for (; e < num_rows && row_splits[e] <= block_last; e++) {
@@ -373,31 +368,52 @@ assign_kernel(int dims, const float *__restrict__ ccoords, const int *__restrict
             __syncthreads();
             if (threadIdx.x < nt) {
                 const int t = threadIdx.x;
-                for (int d = 0; d < dims; d++) s_c[t][d] = cl.centre[(size_t)(off + c0 + t) * dims + d];
-                s_r2[t] = cl.radius_sq[off + c0 + t];
+                Rec<NR> r;
+#pragma unroll
+                for (int d = 0; d < NR * 4; d++) r.v[d] = 0.f;
+#pragma unroll
+                for (int d = 0; d < rec_dims<NR>(); d++)
+                    if (d < dims) r.v[d] = cl.centre[(size_t)(off + c0 + t) * dims + d];
+                const int lonely = cl.lonely[off + c0 + t];
+                r.v[rec_r2_slot<NR>()] = lonely ? -1.f : cl.radius_sq[off + c0 + t];
+#pragma unroll
+                for (int u = 0; u < NR; u++)
+                    s_rec[t][u] = make_float4(r.v[4 * u], r.v[4 * u + 1], r.v[4 * u + 2], r.v[4 * u + 3]);
                 s_pos[t] = cl.subset_pos[off + c0 + t];
-                s_lonely[t] = cl.lonely[off + c0 + t];
+                s_lonely[t] = lonely;
             }
             __syncthreads();
             if (done) continue;
-            for (int c = 0; c < nt; c++) {
-                bool covered;
-                float dsq = 0.f;
-                if (s_lonely[c]) {
-                    covered = s_pos[c] == my_filtered;
-                    if (covered && !by_max_beta) dsq = centre_distsq(s_c[c], x, dims);
-                } else {
-                    dsq = centre_distsq(s_c[c], x, dims);
-                    covered = my_mask == 0 && dsq <= s_r2[c];
+            if (my_mask != 0) {
+                // only a masked condensate at this very hit covers it
+                for (int c = 0; c < nt; c++) {
+                    if (!s_lonely[c] || s_pos[c] != my_filtered) continue;
+                    if (by_max_beta) {
+                        best = c0 + c; best_off = off;
+                        done = true;
+                        break;
+                    }
+                    const Rec<NR> r = load_rec_shared<NR>(s_rec[c]);
+                    const float dsq = rec_distsq<NR>(r, x, dims);
+                    if (__fmul_rn(min_distance, cl.radius_sq[off + c0 + c]) >= dsq) {
+                        best = c0 + c; best_off = off;
+                        min_distance = dsq;
+                    }
                 }
-                if (!covered) continue;
+                continue;
+            }
+            for (int c = 0; c < nt; c++) {
+                const Rec<NR> r = load_rec_shared<NR>(s_rec[c]);
+                const float dsq = rec_distsq<NR>(r, x, dims);
+                const float r2 = r.v[rec_r2_slot<NR>()];
+                if (!(dsq <= r2)) continue;
                 if (by_max_beta) {
-                    best = c0 + c; best_pos = s_pos[c];
+                    best = c0 + c; best_off = off;
                     done = true;
                     break;
                 }
-                if (__fmul_rn(min_distance, s_r2[c]) >= dsq) {
-                    best = c0 + c; best_pos = s_pos[c];
+                if (__fmul_rn(min_distance, r2) >= dsq) {
+                    best = c0 + c; best_off = off;
                     min_distance = dsq;
                 }
             }
@@ -405,7 +421,7 @@ assign_kernel(int dims, const float *__restrict__ ccoords, const int *__restrict
     }
     if (live && best >= 0) {
         assignment[v] = best;
-        association[v] = original_indices_h[best_pos];
+        association[v] = original_indices_h[cl.subset_pos[best_off + best]];
     }
 }
 
@@ -516,10 +532,15 @@ extern "C" int hgc_binned_assign_to_condensates(
     condensate_totals_kernel<<<1, 32, 0, stream>>>(b.cl.count, num_rows, d_n_condensates);
     HGC_LAUNCH_CHECK();
     if (n_vert > 0 && n_vert_h > 0 && num_rows > 0) {
-        assign_kernel<<<div_up(n_vert, kAssignThreads), kAssignThreads, 0, stream>>>(
-                dimensions, d_ccoords, d_no_condensation_mask, d_indices_to_filtered, d_original_indices_h,
-                d_row_splits, d_row_splits_h, num_rows, n_vert, assign_by_max_beta != 0, b.cl, d_assignment,
-                d_association);
+#define HGC_ASSIGN(NR)                                                                                         \
+    assign_kernel<NR><<<div_up(n_vert, kAssignThreads), kAssignThreads, 0, stream>>>(                            \
+            dimensions, d_ccoords, d_no_condensation_mask, d_indices_to_filtered, d_original_indices_h,          \
+            d_row_splits, d_row_splits_h, num_rows, n_vert, assign_by_max_beta != 0, b.cl, d_assignment,         \
+            d_association)
+        if (dimensions <= 3) HGC_ASSIGN(1);
+        else if (dimensions <= 7) HGC_ASSIGN(2);
+        else HGC_ASSIGN(3);
+#undef HGC_ASSIGN
         HGC_LAUNCH_CHECK();
     }
     return HGC_OK;

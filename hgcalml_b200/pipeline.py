@@ -29,6 +29,8 @@ class KnnAccumulatePipeline:
         self.s_run = torch.cuda.Stream(self.device)
         self.s_d2h = torch.cuda.Stream(self.device)
         self._slots = None
+        self._rs_pinned = None
+        self._h2d_done = None
 
     def _ensure_slots(self, max_hits, n_coords, n_feat, max_events):
         ok = (self._slots is not None and self._slots[0]["coords"].shape[0] >= max_hits
@@ -58,7 +60,16 @@ class KnnAccumulatePipeline:
         start = torch.cuda.current_stream(self.device)
         for s in (self.s_h2d, self.s_run, self.s_d2h):
             s.wait_stream(start)
-        rs_chunks = [torch.from_numpy((rs[e0:e1 + 1] - rs[e0]).astype(np.int32)).pin_memory() for e0, e1 in chunks]
+        # row splits of all chunks, rebased to their chunk, in one pinned buffer that is kept between calls
+        width = self.events_per_chunk + 1
+        if self._rs_pinned is None or self._rs_pinned.shape[0] < len(chunks):
+            self._rs_pinned = torch.empty((max(len(chunks), 1), width), dtype=torch.int32).pin_memory()
+        if self._h2d_done is not None:
+            self._h2d_done.synchronize()  # the previous call's copies out of this buffer have finished
+        rs_host = self._rs_pinned.numpy()
+        for c, (e0, e1) in enumerate(chunks):
+            rs_host[c, :e1 - e0 + 1] = rs[e0:e1 + 1] - rs[e0]
+        rs_chunks = [self._rs_pinned[c, :e1 - e0 + 1] for c, (e0, e1) in enumerate(chunks)]
         for c, (e0, e1) in enumerate(chunks):
             slot = self._slots[c % self.n_slots]
             lo, hi = int(rs[e0]), int(rs[e1])
@@ -82,6 +93,8 @@ class KnnAccumulatePipeline:
                 self.s_d2h.wait_event(done)
                 out[lo:hi].copy_(res, non_blocking=True)
                 res.record_stream(self.s_d2h)
+        self._h2d_done = torch.cuda.Event()
+        self._h2d_done.record(self.s_h2d)
         start.wait_stream(self.s_d2h)
         start.wait_stream(self.s_run)
         start.wait_stream(self.s_h2d)
