@@ -50,6 +50,8 @@ typedef double knn_key;
 #ifndef HGC_KNN_OFFER2
 #define HGC_KNN_OFFER2 1
 #endif
+static_assert(HGC_KNN_FLUSH_AT >= 1 && HGC_KNN_FLUSH_AT <= 32,
+              "a candidate step parks up to 32 keys on top of fewer than HGC_KNN_FLUSH_AT in a 64-slot buffer");
 #ifndef HGC_KNN_MIN_BLOCKS
 #define HGC_KNN_MIN_BLOCKS 4
 #endif
