@@ -17,13 +17,13 @@ namespace {
 #define HGC_ACC_CH16 4
 #endif
 #ifndef HGC_ACC_MINB16
-#define HGC_ACC_MINB16 5
+#define HGC_ACC_MINB16 4
 #endif
 #ifndef HGC_ACC_THREADS
 #define HGC_ACC_THREADS 256
 #endif
 #ifndef HGC_ACC_TILE
-#define HGC_ACC_TILE 256
+#define HGC_ACC_TILE 512
 #endif
 constexpr int kAccThreads = HGC_ACC_THREADS;
 constexpr int kAccTile = HGC_ACC_TILE;  // consecutive hits a block processes before it jumps to its next tile
@@ -292,8 +292,10 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
 #define HGC_VEC(L, V, C, M) return launch_vec<L, V, C, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, ldk, F4, n_out, mm, order, scale, sub_self, stream)
     if (F4 <= 4) HGC_VEC(4, 1, 4, 3);
     if (F4 <= 8) HGC_VEC(8, 1, 4, 3);
-    // F = 64: 16 lanes per hit, 4 rows in flight, 5 blocks per SM (51 registers) measured best of
-    // {rows in flight / blocks per SM: 8/2, 8/3, 4/3, 4/4, 4/5, 2/4, 2/5, 2/6}; tiles of 256 hits best of 64..2048
+    // F = 64: 16 lanes per hit, 4 rows in flight, 4 blocks per SM (64 registers), tiles of 512 hits:
+    // measured best on the 64-event batch of {rows in flight / blocks per SM: 8/2, 8/3, 4/3, 4/4, 4/5, 2/4,
+    // 2/5, 2/6} and of tiles of 64..2048 hits.  (On a batch of 8 events run back to back, 5 blocks per SM
+    // and tiles of 256 looked 6 % faster; on the full batch they are 5 % slower.)
     if (F4 <= 16) HGC_VEC(16, 1, HGC_ACC_CH16, HGC_ACC_MINB16);
     if (F4 <= 32) HGC_VEC(32, 1, 4, 3);
     if (F4 <= 64) HGC_VEC(32, 2, 4, 2);
