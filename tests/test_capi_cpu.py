@@ -92,3 +92,41 @@ def test_tf_shims_type_check_against_api_stub():
                         os.path.join(ROOT, "hgcalml_b200", "tf_shims", "hgc_tf_ops.cc")],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_host_side_validation_of_wrapper_level_entries():
+    """Argument rules of the wrapper-level entries are checked on the host, before any CUDA call."""
+    from hgcalml_b200 import _capi
+    L = _capi.lib
+    nul = ctypes.c_void_p(None)
+    f = ctypes.c_float
+    # gravnet collect: the slice must fit the rows, the output row must hold 2F columns
+    assert L.hgc_gravnet_collect(nul, nul, 8, 1, 8, nul, nul, 64, nul, 10, 16, f(10.), 1, nul, nul) == -1
+    assert L.hgc_gravnet_collect(nul, nul, 9, 1, 8, nul, nul, 31, nul, 10, 16, f(10.), 1, nul, nul) == -1
+    assert L.hgc_gravnet_collect(nul, nul, 9, -1, 8, nul, nul, 32, nul, 10, 16, f(10.), 1, nul, nul) == -1
+    assert L.hgc_gravnet_collect(nul, nul, 9, 1, 8, nul, nul, 32, nul, 0, 16, f(10.), 1, nul, nul) == 0  # no hits
+    # condensate wrapper: assert-rules of modules/assign_condensate_op.py:245-247
+    args = lambda **kw: [nul] * 11 + [kw.get("n", 10), kw.get("dims", 3), kw.get("n_rs", 2), f(kw.get("bt", 0.1)),
+                                      f(kw.get("dt", 1.0)), 1, kw.get("nbd", 3), nul, 0, nul]
+    assert L.hgc_build_and_assign_condensates(*args(nbd=0)) == -1
+    assert L.hgc_build_and_assign_condensates(*args(nbd=7)) == -1
+    assert L.hgc_build_and_assign_condensates(*args(bt=1.5)) == -1
+    assert L.hgc_build_and_assign_condensates(*args(dt=0.0)) == -1
+    assert L.hgc_build_and_assign_condensates(*args(dims=9)) == -3
+    assert L.hgc_build_and_assign_condensates(*args()) == -1           # null outputs
+    assert L.hgc_build_and_assign_condensates_workspace_bytes(1000, 3, 3, 3) > 0
+    assert L.hgc_build_and_assign_condensates_workspace_bytes(1000, 9, 3, 3) == 0
+
+
+def test_gravnet_layer_mirrors_construct_without_gpu():
+    import torch
+    from hgcalml_b200 import _capi
+    from hgcalml_b200.GravNetLayersRagged import RaggedGravNet, DistanceWeightedMessagePassing, collect_neighbours
+    layer = RaggedGravNet(n_neighbours=8, n_dimensions=3, n_filters=12, n_propagate=6, n_in=10)
+    assert layer.output_feature_transform.kernel.shape == (2 * 6 + 10, 12)
+    mp = DistanceWeightedMessagePassing([4, 5], n_in=10)
+    assert [tuple(d.kernel.shape) for d in mp.feature_tranformation_dense] == [(10, 4), (8, 5)]
+    with pytest.raises(NotImplementedError):
+        RaggedGravNet(8, 3, 12, 6, n_in=10, sumwnorm=True)
+    with pytest.raises(_capi.HgcError):  # CPU tensors: no fallback
+        collect_neighbours(torch.zeros(4, 4), torch.zeros(4, 3, dtype=torch.int32), torch.zeros(4, 3))
