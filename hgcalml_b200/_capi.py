@@ -54,6 +54,7 @@ def _load():
         "hgc_push_knn_grad": (I, [P] * 6 + [I] * 3 + [P]),
         "hgc_knn_grad_workspace_bytes": (S, [I, I]),
         "hgc_accumulate_knn_grad": (I, [P] * 7 + [I] * 6 + [P, S, P]),
+        "hgc_accumulate_knn_grad_ordered": (I, [P] * 7 + [I] * 6 + [P, P, S, P]),
         "hgc_select_knn_grad": (I, [P] * 5 + [I] * 3 + [P, S, P]),
         "hgc_binned_assign_to_condensates_workspace_bytes": (S, [I] * 4),
         "hgc_binned_assign_to_condensates": (I, [I, I] + [P] * 4 + [P] + [P] * 2 + [P] * 4 + [P] * 4 + [P] * 3

@@ -61,10 +61,12 @@ def AccumulateKnn(distances, features, indices, mean_and_max=True, force_tf=Fals
     return out, maxidx
 
 
-def AccumulateKnnGrad(grad_from_out_features, distances, features, neigh_indices, max_feat_indices):
+def AccumulateKnnGrad(grad_from_out_features, distances, features, neigh_indices, max_feat_indices, order=None):
     """The registered op ``AccumulateKnnGrad`` (modules/compiled/accumulate_knn_grad_module.cc:7-15), the
     gradient the reference attaches to the op ``AccumulateKnn`` (modules/accknn_op.py:71-90).
-    ``distances`` are the forward op's weights.  Returns ``(grad_distances [N,K], grad_features [N,F])``;
+    ``distances`` are the forward op's weights.  ``order`` (optional int32 permutation of the hits, e.g.
+    the sorting of ``BinnedSelectKnn``) only sets the order in which hits are processed.
+    Returns ``(grad_distances [N,K], grad_features [N,F])``;
     mean-and-max mode is detected from the width of the incoming gradient, as in the reference."""
     C.require_cuda(grad_from_out_features, distances, features, neigh_indices)
     g, w, feat = C.f32(grad_from_out_features), C.f32(distances), C.f32(features)
@@ -81,9 +83,13 @@ def AccumulateKnnGrad(grad_from_out_features, distances, features, neigh_indices
     gw = torch.empty((n, k), dtype=torch.float32, device=dev)
     gf = torch.empty((n, f), dtype=torch.float32, device=dev)
     ws = C.workspace(C.lib.hgc_knn_grad_workspace_bytes(n, k), dev)
-    C.check(C.lib.hgc_accumulate_knn_grad(C.ptr(g), C.ptr(w), C.ptr(feat), C.ptr(maxidx), C.ptr(idx),
-                                          C.ptr(gw), C.ptr(gf), n, k, f, g.shape[1], 0, int(mean_and_max),
-                                          C.ptr(ws), ws.numel(), C.stream_of(feat)), "AccumulateKnnGrad")
+    if order is not None:
+        C.require_cuda(order)
+        order = C.i32(order)
+    C.check(C.lib.hgc_accumulate_knn_grad_ordered(C.ptr(g), C.ptr(w), C.ptr(feat), C.ptr(maxidx), C.ptr(idx),
+                                                  C.ptr(gw), C.ptr(gf), n, k, f, g.shape[1], 0, int(mean_and_max),
+                                                  C.ptr(order), C.ptr(ws), ws.numel(), C.stream_of(feat)),
+            "AccumulateKnnGrad")
     return gw, gf
 
 
@@ -91,20 +97,22 @@ class _AccumulateLinKnnFunction(torch.autograd.Function):
     """AccumulateLinKnn with the reference's gradient wired into torch autograd."""
 
     @staticmethod
-    def forward(ctx, weights, features, indices, mean_and_max):
+    def forward(ctx, weights, features, indices, mean_and_max, order):
         out, maxidx = AccumulateLinKnn(weights, features, indices, mean_and_max=mean_and_max)
         ctx.save_for_backward(weights, features, indices, maxidx)
+        ctx.order = order
         ctx.mark_non_differentiable(maxidx)
         return out, maxidx
 
     @staticmethod
     def backward(ctx, grad_out, _grad_maxidx):
         weights, features, indices, maxidx = ctx.saved_tensors
-        gw, gf = AccumulateKnnGrad(grad_out.contiguous(), weights, features, indices, maxidx)
-        return gw, gf, None, None
+        gw, gf = AccumulateKnnGrad(grad_out.contiguous(), weights, features, indices, maxidx, order=ctx.order)
+        return gw, gf, None, None, None
 
 
-def AccumulateKnnDifferentiable(distances, features, indices, mean_and_max=True):
+def AccumulateKnnDifferentiable(distances, features, indices, mean_and_max=True, order=None):
     """``AccumulateKnn`` as the reference's training path sees it: ``exp(-distances)`` as a
-    differentiable tensor op, then the op with its registered gradient (modules/accknn_op.py:52-57,71-90)."""
-    return _AccumulateLinKnnFunction.apply(torch.exp(-distances), features, indices, mean_and_max)
+    differentiable tensor op, then the op with its registered gradient (modules/accknn_op.py:52-57,71-90).
+    ``order``: optional processing order for the backward pass (see ``AccumulateKnnGrad``)."""
+    return _AccumulateLinKnnFunction.apply(torch.exp(-distances), features, indices, mean_and_max, order)

@@ -10,6 +10,7 @@
 // reference's CPU loop, so the result is bit-identical to it.
 #include "common.cuh"
 #include "incoming.cuh"
+#include "../../include/hgcalml_b200.h"
 
 namespace hgc {
 namespace {
@@ -31,38 +32,71 @@ __global__ void __launch_bounds__(256)
 acc_grad_features_kernel(const float *__restrict__ grad_out, const float *__restrict__ weights,
                          const int *__restrict__ max_idx, const int *__restrict__ nidx,
                          const int *__restrict__ bounds, const int *__restrict__ sedges,
-                         float *__restrict__ grad_feat, int n_vert, int K, int F, int G, bool mean_and_max)
+                         float *__restrict__ grad_feat, int n_vert, int K, int F, int G, bool mean_and_max,
+                         const int *__restrict__ order)
 {
     const int lane = threadIdx.x & 31;
-    const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (m >= n_vert) return;
+    const int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (slot >= n_vert) return;
+    const int m = order ? order[slot] : slot;  // processing order only: every target is visited once
     const int e_begin = bounds[m], e_end = bounds[m + 1];
     const float kf = (float)K;
+    constexpr int U = 4;  // edges whose rows are requested together (the sum still runs edge by edge)
     for (int f0 = 0; f0 < F; f0 += 32 * FPL) {
         float acc[FPL];
 #pragma unroll
         for (int u = 0; u < FPL; u++) acc[u] = 0.f;
-        for (int p = e_begin; p < e_end; p++) {
-            const int e = sedges[p];
-            const int i = e / K, k = e - i * K;
-            const float w = weights[e];
-            bool counts_for_max = true;
-            if (i == m) {
-                // the hit is its own neighbour: only its first occurrence in the row counts for the max
-                bool earlier = false;
-                for (int kk = lane; kk < k; kk += 32) earlier = earlier || nidx[(size_t)i * K + kk] == i;
-                counts_for_max = !__any_sync(0xffffffffu, earlier);
-            }
+        for (int pw = e_begin; pw < e_end; pw += 32) {
+            // the warp fetches 32 edges and their weights at once, then hands them round by shuffle
+            const int my_p = pw + lane;
+            const int my_e = my_p < e_end ? sedges[my_p] : 0;
+            const float my_w = my_p < e_end ? weights[my_e] : 0.f;
+            const int n_here = min(32, e_end - pw);
+            for (int q0 = 0; q0 < n_here; q0 += U) {
+                int ii[U];
+                float ww[U], g[U][FPL];
+                int am[U][FPL];
 #pragma unroll
-            for (int u = 0; u < FPL; u++) {
-                const int f = f0 + u * 32 + lane;
-                if (f < F) {
-                    const float g = grad_out[(size_t)i * G + f];
-                    const float mean_part = __fmul_rn(__fdiv_rn(g, kf), w);
-                    float max_part = 0.f;
-                    if (mean_and_max && counts_for_max && max_idx[(size_t)i * F + f] == m)
-                        max_part = __fmul_rn(grad_out[(size_t)i * G + F + f], w);
-                    acc[u] = __fadd_rn(acc[u], __fadd_rn(mean_part, max_part));
+                for (int q = 0; q < U; q++) {
+                    const int src = min(q0 + q, n_here - 1);
+                    const int e = __shfl_sync(0xffffffffu, my_e, src);
+                    ww[q] = __shfl_sync(0xffffffffu, my_w, src);
+                    ii[q] = e / K;
+#pragma unroll
+                    for (int u = 0; u < FPL; u++) {
+                        const int f = f0 + u * 32 + lane;
+                        g[q][u] = 0.f;
+                        am[q][u] = -1;
+                        if (f < F) {
+                            g[q][u] = grad_out[(size_t)ii[q] * G + f];
+                            if (mean_and_max) am[q][u] = max_idx[(size_t)ii[q] * F + f];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < U; q++) {
+                    if (q0 + q >= n_here) break;  // uniform
+                    const int i = ii[q];
+                    const float w = ww[q];
+                    bool counts_for_max = true;
+                    if (i == m) {
+                        // the hit is its own neighbour: only its first occurrence in the row counts for the max
+                        const int k = __shfl_sync(0xffffffffu, my_e, q0 + q) - i * K;
+                        bool earlier = false;
+                        for (int kk = lane; kk < k; kk += 32) earlier = earlier || nidx[(size_t)i * K + kk] == i;
+                        counts_for_max = !__any_sync(0xffffffffu, earlier);
+                    }
+#pragma unroll
+                    for (int u = 0; u < FPL; u++) {
+                        const int f = f0 + u * 32 + lane;
+                        if (f < F) {
+                            const float mean_part = __fmul_rn(__fdiv_rn(g[q][u], kf), w);
+                            float max_part = 0.f;
+                            if (mean_and_max && counts_for_max && am[q][u] == m)
+                                max_part = __fmul_rn(grad_out[(size_t)i * G + F + f], w);
+                            acc[u] = __fadd_rn(acc[u], __fadd_rn(mean_part, max_part));
+                        }
+                    }
                 }
             }
         }
@@ -81,13 +115,15 @@ __global__ void __launch_bounds__(256)
 acc_grad_weights_kernel(const float *__restrict__ grad_out, const float *__restrict__ feat,
                         const int *__restrict__ max_idx, const int *__restrict__ nidx,
                         float *__restrict__ grad_w, long long n_edges, int n_vert, int K, int F, int G,
-                        bool mean_and_max, bool vec4)
+                        bool mean_and_max, bool vec4, const int *__restrict__ order)
 {
-    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n_edges) return;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_edges) return;
+    const int row = (int)(t / K);
+    const int i = order ? order[row] : row;  // processing order only
+    const long long e = (long long)i * K + (t - (long long)row * K);
     const int m = nidx[e];
     if (m < 0 || m >= n_vert) { grad_w[e] = 0.f; return; }
-    const int i = (int)(e / K);
     const float *g = grad_out + (size_t)i * G;
     const float *x = feat + (size_t)m * F;
     const int *am = max_idx + (size_t)i * F;
@@ -194,6 +230,19 @@ extern "C" int hgc_accumulate_knn_grad(
         int n_vert, int n_neigh, int n_feat, int n_grad_from_out_feat, int n_moments, int mean_and_max,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream_)
 {
+    return hgc_accumulate_knn_grad_ordered(d_grad_from_out_features, d_distances, d_feat, d_max_feat_indices,
+                                           d_neigh_indices, d_out_grad_distances, d_out_grad_features, n_vert,
+                                           n_neigh, n_feat, n_grad_from_out_feat, n_moments, mean_and_max,
+                                           nullptr, workspace, workspace_bytes, stream_);
+}
+
+extern "C" int hgc_accumulate_knn_grad_ordered(
+        const float *d_grad_from_out_features, const float *d_distances, const float *d_feat,
+        const int *d_max_feat_indices, const int *d_neigh_indices,
+        float *d_out_grad_distances, float *d_out_grad_features,
+        int n_vert, int n_neigh, int n_feat, int n_grad_from_out_feat, int n_moments, int mean_and_max,
+        const int *d_order, void *workspace, size_t workspace_bytes, hgc_stream_t stream_)
+{
     (void)n_moments;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (int rc = check_edge_count(n_vert, n_neigh)) return rc;
@@ -218,7 +267,7 @@ extern "C" int hgc_accumulate_knn_grad(
 #define HGC_FEAT(FPL)                                                                               \
     acc_grad_features_kernel<FPL><<<div_up(n_vert, 8), 256, 0, stream>>>(                           \
             d_grad_from_out_features, d_distances, d_max_feat_indices, d_neigh_indices, b.bounds, b.sedges, \
-            d_out_grad_features, n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0)
+            d_out_grad_features, n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0, d_order)
         if (n_feat <= 32) HGC_FEAT(1);
         else if (n_feat <= 64) HGC_FEAT(2);
         else HGC_FEAT(4);
@@ -231,7 +280,7 @@ extern "C" int hgc_accumulate_knn_grad(
                       (!mean_and_max || aligned16(d_max_feat_indices));
     acc_grad_weights_kernel<<<div_up(ne, 256), 256, 0, stream>>>(
             d_grad_from_out_features, d_feat, d_max_feat_indices, d_neigh_indices, d_out_grad_distances, ne,
-            n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0, vec4);
+            n_vert, n_neigh, n_feat, n_grad_from_out_feat, mean_and_max != 0, vec4, d_order);
     HGC_LAUNCH_CHECK();
     return HGC_OK;
 }

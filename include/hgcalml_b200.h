@@ -274,6 +274,17 @@ int hgc_accumulate_knn_grad(
         float *d_out_grad_distances, float *d_out_grad_features,
         int n_vert, int n_neigh, int n_feat, int n_grad_from_out_feat, int n_moments, int mean_and_max,
         void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+
+/* The same gradient with a processing order: d_order (may be NULL) is a permutation of the hits,
+ * e.g. the bin-sorting permutation that hgc_binned_select_knn_ragged returns.  Results do not depend
+ * on it (every target sums its incoming edges in (hit, slot) order); with spatially close hits next
+ * to each other the gathered rows of consecutive hits overlap and are found in cache. */
+int hgc_accumulate_knn_grad_ordered(
+        const float *d_grad_from_out_features, const float *d_distances, const float *d_feat,
+        const int *d_max_feat_indices, const int *d_neigh_indices,
+        float *d_out_grad_distances, float *d_out_grad_features,
+        int n_vert, int n_neigh, int n_feat, int n_grad_from_out_feat, int n_moments, int mean_and_max,
+        const int *d_order, void *workspace, size_t workspace_bytes, hgc_stream_t stream);
 int hgc_select_knn_grad(
         const float *d_grad_dist, const int *d_indices, const float *d_dist, const float *d_coord,
         float *d_grad_coord, int n_vert, int n_neigh, int n_coords,

@@ -537,3 +537,20 @@ def test_condensates_one_call_empty_batch(cuda):
     z = torch.zeros((0, 3), device=cuda)
     out = BuildAndAssignCondensatesBinned(z, z[:, :1], z[:, :1], torch.zeros(3, dtype=torch.int32, device=cuda), 0.1)
     assert out[0].shape == (0, 1) and out[2].numel() == 0 and N(out[4]).tolist() == [0, 0, 0]
+
+
+def test_accumulate_knn_grad_order_is_only_a_schedule(cuda):
+    """The ordered gradient entry gives bit-identical results for any processing order."""
+    from hgcalml_b200.accknn_op import AccumulateLinKnn, AccumulateKnnGrad
+    from hgcalml_b200.binned_select_knn_op import BinnedSelectKnn
+    c, f, rs = synth.shower_batch([5000, 0, 3000], dims=4, n_feat=24, seed=91)
+    idx, d2, sorting = BinnedSelectKnn(20, T(c, cuda), T(rs, cuda), return_sorting=True)
+    w = torch.exp(-10. * d2)
+    ft = T(f, cuda)
+    out, maxidx = AccumulateLinKnn(w, ft, idx)
+    g = torch.randn(out.shape, generator=torch.Generator(device="cpu").manual_seed(3)).to(cuda)
+    ref = AccumulateKnnGrad(g, w, ft, idx, maxidx)
+    perm = torch.randperm(len(c), generator=torch.Generator(device="cpu").manual_seed(4)).to(cuda).to(torch.int32)
+    for order in (sorting, perm):
+        got = AccumulateKnnGrad(g, w, ft, idx, maxidx, order=order)
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
