@@ -327,17 +327,21 @@ public:
         OP_REQUIRES_OK(c, c->GetAttr("subtract_self", &subtract_self_));
     }
     void Compute(OpKernelContext *ctx) override {
-        const Tensor &dist = ctx->input(0), &feat = ctx->input(1), &idx = ctx->input(2);
+        const Tensor &dist = ctx->input(0), &feat = ctx->input(1), &idx = ctx->input(2), &order = ctx->input(3);
         const int n_vert = feat.dim_size(0), F = feat.dim_size(1), ld = idx.dim_size(1);
         OP_REQUIRES(ctx, dist.dim_size(0) == n_vert && idx.dim_size(0) == n_vert && dist.dim_size(1) == ld,
                     errors::InvalidArgument("HgcGravnetCollect expects matching first dimensions and neighbour counts."));
+        // order: the sorting output of HgcBinnedSelectKnnRagged, or an empty tensor for the caller's order
+        OP_REQUIRES(ctx, order.dim_size(0) == n_vert || order.dim_size(0) == 0,
+                    errors::InvalidArgument("HgcGravnetCollect expects an order of length nvert or an empty one."));
         Tensor *out, *maxidx;
         OP_REQUIRES_OK(ctx, ctx->allocate_output(0, {n_vert, 2 * F}, &out));
         OP_REQUIRES_OK(ctx, ctx->allocate_output(1, {n_vert, F}, &maxidx));
         OP_REQUIRES_OK(ctx, FromHgc(hgc_gravnet_collect(
             dist.flat<float>().data(), idx.flat<int>().data(), ld, first_slot_, ld - first_slot_,
             feat.flat<float>().data(), out->flat<float>().data(), 2 * F, maxidx->flat<int>().data(), n_vert, F,
-            scale_, subtract_self_, nullptr, StreamOf(ctx)), "HgcGravnetCollect"));
+            scale_, subtract_self_, order.dim_size(0) == n_vert ? order.flat<int>().data() : nullptr, StreamOf(ctx)),
+            "HgcGravnetCollect"));
     }
 private:
     int first_slot_;
