@@ -35,7 +35,9 @@ UNIT = "hits/s"
 # DRAM traffic per hit of the two main kernels at K = F = 64, 4 coordinates, from the ncu capture
 # summarised in profiles/select_knn_and_accumulate_2events_full.md (traffic grows with the hits).
 ACC_DRAM_BYTES_PER_HIT = 1972
-KNN_DRAM_BYTES_PER_HIT = 408
+KNN_DRAM_BYTES_PER_HIT = 409
+KNN_ISSUE_ACTIVE_PCT = 75.4
+KNN_WARP_INSTR_PER_QUERY = 5020
 
 
 def parse():
@@ -319,8 +321,16 @@ def main():
                    "unit": "GB/s", "peak_kind": peak_kind, "traffic": int(n * KNN_DRAM_BYTES_PER_HIT) if (K, F) == (64, 64) else None,
                    "traffic_source": "ncu dram__bytes_read+write of a 400k-hit launch, scaled by hits",
                    "ms_per_launch": kernel_times["select_knn_ms"], "algorithmic_bytes": knn_bytes,
-                   "note": "the search is bound by FP32 issue and shuffles, not by HBM; the HBM figure is "
-                           "reported because it is the dominant kernel by time"}
+                   "note": "the search is bound by instruction issue (sorting networks on shuffles), not by "
+                           "HBM; the HBM figure is reported because it is the dominant kernel by time",
+                   # what bounds it instead, from the ncu capture of a 400k-hit launch (profiles/): issue
+                   # slots in use, and warp instructions per query against the SMs' issue rate at the
+                   # sampled clock
+                   "issue": {"ncu_issue_active_pct": KNN_ISSUE_ACTIVE_PCT,
+                             "ncu_warp_instructions_per_query": KNN_WARP_INSTR_PER_QUERY,
+                             "issue_bound_ms": n * KNN_WARP_INSTR_PER_QUERY
+                                               / (148 * 4 * float((clocks or {}).get("sm_mhz") or 1965.0) * 1e6) * 1e3
+                             if (K, F) == (64, 64) else None}}
             knn["frac"] = knn["achieved"] / hbm_peak
             dominant = knn if kernel_times["select_knn_ms"] >= kernel_times["accumulate_ms"] else acc
             line["roofline"] = dominant
