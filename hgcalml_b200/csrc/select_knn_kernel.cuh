@@ -13,15 +13,16 @@
 //    is skipped when the box's distance to the query already exceeds the current K-th best: with
 //    the same unfused subtract/multiply/add sequence as the point distance, rounding is monotone,
 //    so no point of the chunk can have a smaller computed distance than the box.
-//  * Short ranges (sparse regions) are laid end to end and walked 32 candidates at a time.
+//  * Short ranges (sparse regions) are laid end to end and walked 64 candidates at a time, two per
+//    lane, so that two coordinate loads are in flight per lane.
 //  * From the second shell on, bins whose distance to the query's bin already puts them beyond the
 //    K-th best are left out of the ranges (the shells are cubes, the K-th best cuts a ball).
 //
 // The best K-1 candidates live in registers as a sorted list striped over the lanes (rank r in
 // register r/32 of lane r%32), keyed by (distance bits, index) in one 64-bit word so that ties
 // fall to the lower index.  Candidates that beat the current K-th best are parked in a per-warp
-// shared-memory buffer of 32; a full buffer is sorted with a warp-shuffle bitonic network and
-// merged into the list.  Distances are computed with separately rounded operations in coordinate
+// shared-memory buffer of 64 slots; as soon as 32 are parked they are sorted with a warp-shuffle
+// bitonic network and merged into the list, and the rest is filtered against the new K-th best.  Distances are computed with separately rounded operations in coordinate
 // order, so they are bit-identical to the CPU op (binned_select_knn_kernel.cc:19-29).
 #pragma once
 #include "common.cuh"
