@@ -507,7 +507,8 @@ def test_push_knn_grad_vs_checker_and_autograd(cuda, oracle):
     assert torch.equal(wt.grad, gw) and torch.equal(ft.grad, gf)
 
 
-@pytest.mark.parametrize("dims,nbin_dims,thr", [(3, 3, 1.0), (2, 3, 0.7), (4, 2, 1.3), (3, 1, 0.5)])
+@pytest.mark.parametrize("dims,nbin_dims,thr", [(3, 3, 1.0), (2, 3, 0.7), (4, 2, 1.3), (3, 1, 0.5), (7, 3, 1.0),
+                                                (8, 2, 2.0), (1, 1, 1.0)])
 def test_condensates_one_call_equals_stepwise_and_checker(cuda, oracle, dims, nbin_dims, thr):
     """The one-call wrapper, the stepwise tensor-op wrapper around the op, and the checker agree
     bit for bit, with a distance threshold, fewer binned dimensions, a mask and empty events."""
