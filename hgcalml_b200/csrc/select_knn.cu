@@ -3,6 +3,14 @@
 #include "common.cuh"
 #include "select_knn.cuh"
 
+// ranges longer than this many hits are scanned chunk-wise with box tests; grid size per SM
+#ifndef HGC_KNN_LONG_RANGE
+#define HGC_KNN_LONG_RANGE 96
+#endif
+#ifndef HGC_KNN_GRID_BLOCKS_PER_SM
+#define HGC_KNN_GRID_BLOCKS_PER_SM 4
+#endif
+
 namespace hgc {
 namespace {
 
@@ -87,9 +95,9 @@ int launch_select_knn(const KnnScratch &s, int n_coords, const int *bin_idx, con
     a.n_vert = n_vert; a.K = K; a.n_bboundaries = n_bboundaries; a.tf_compat = tf_compat;
     a.status = status;
     a.work_counter = status + 16;  // inside the 256 zeroed bytes that start every workspace
-    a.long_range = 96;
+    a.long_range = HGC_KNN_LONG_RANGE;
     a.fetch = 1;
-    a.blocks_per_sm = 4;
+    a.blocks_per_sm = HGC_KNN_GRID_BLOCKS_PER_SM;
     a.stats = nullptr;
 #ifdef HGC_KNN_STATS
     {
