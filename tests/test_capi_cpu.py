@@ -130,3 +130,24 @@ def test_gravnet_layer_mirrors_construct_without_gpu():
         RaggedGravNet(8, 3, 12, 6, n_in=10, sumwnorm=True)
     with pytest.raises(_capi.HgcError):  # CPU tensors: no fallback
         collect_neighbours(torch.zeros(4, 4), torch.zeros(4, 3, dtype=torch.int32), torch.zeros(4, 3))
+
+
+def _build_c_user(out_path):
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    cuda = "/usr/local/cuda"
+    if gcc is None or not os.path.exists(os.path.join(cuda, "include", "cuda_runtime_api.h")):
+        pytest.skip("needs gcc and the CUDA runtime headers")
+    pkg = os.path.join(ROOT, "hgcalml_b200")
+    r = subprocess.run([gcc, "-std=c11", "-O2", "-ffp-contract=off", "-I" + os.path.join(ROOT, "include"),
+                        "-I" + os.path.join(cuda, "include"), os.path.join(ROOT, "tests", "c_abi", "knn_from_c.c"),
+                        "-o", out_path, "-L" + pkg, "-lhgcalml_b200", "-L" + os.path.join(cuda, "lib64"), "-lcudart",
+                        "-lm", "-Wl,-rpath," + pkg], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    return out_path
+
+
+def test_plain_c_user_of_the_abi_compiles_and_links(tmp_path):
+    """The header is C (not C++) and the library links into a program that knows nothing of Python or torch."""
+    _build_c_user(str(tmp_path / "knn_from_c"))

@@ -555,3 +555,14 @@ def test_accumulate_knn_grad_order_is_only_a_schedule(cuda):
     for order in (sorting, perm):
         got = AccumulateKnnGrad(g, w, ft, idx, maxidx, order=order)
         assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
+
+
+def test_plain_c_user_of_the_abi_runs(cuda, tmp_path):
+    """tests/c_abi/knn_from_c.c: the wrapper-level search and the accumulation called from plain C and
+    checked there against a brute-force loop."""
+    import subprocess
+    from test_capi_cpu import _build_c_user
+    exe = _build_c_user(str(tmp_path / "knn_from_c"))
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.startswith("ok")
