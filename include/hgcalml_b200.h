@@ -9,7 +9,8 @@
  *    (`workspace`, sized by the matching *_workspace_bytes query; 256-byte aligned).
  *  - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call
  *    synchronises the device and no call touches the legacy default stream unless the
- *    caller passes it.
+ *    caller passes it.  Two entries wait for their own stream and say so:
+ *    hgc_workspace_status and hgc_build_and_assign_condensates.
  *  - Return value: HGC_OK or a negative HGC_ERR_* code.  Nothing throws, nothing prints.
  *    Problems that only the device can see (an index outside its table, a bin outside the
  *    grid, an iteration cap reached) set a status word in the workspace, which
