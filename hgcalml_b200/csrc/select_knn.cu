@@ -8,7 +8,7 @@
 #define HGC_KNN_LONG_RANGE 96
 #endif
 #ifndef HGC_KNN_GRID_BLOCKS_PER_SM
-#define HGC_KNN_GRID_BLOCKS_PER_SM 4
+#define HGC_KNN_GRID_BLOCKS_PER_SM 8
 #endif
 
 namespace hgc {

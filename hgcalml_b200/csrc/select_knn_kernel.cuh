@@ -53,8 +53,13 @@ typedef double knn_key;
 #endif
 static_assert(HGC_KNN_FLUSH_AT >= 1 && HGC_KNN_FLUSH_AT <= 32,
               "a candidate step parks up to 32 keys on top of fewer than HGC_KNN_FLUSH_AT in a 64-slot buffer");
+// Resident blocks per SM the kernel is compiled for.  8 blocks of 256 threads leave 32 registers per thread,
+// so part of the state spills to (L1-resident) local memory; measured on the 64-event batch that is still
+// faster than fewer warps with everything in registers (ms per step at 3 / 4 / 5 / 6 / 7 / 8 blocks:
+// 102.0 / 91.7 / 91.4 / 88.8 / 88.0 / 87.8): the kernel is a chain of dependent shuffles and loads, and more
+// warps hide more of their latency.
 #ifndef HGC_KNN_MIN_BLOCKS
-#define HGC_KNN_MIN_BLOCKS 4
+#define HGC_KNN_MIN_BLOCKS 8
 #endif
 constexpr int kKnnWarps = 8;
 constexpr int kKnnThreads = kKnnWarps * kWarp;
