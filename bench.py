@@ -35,9 +35,9 @@ UNIT = "hits/s"
 # DRAM traffic per hit of the two main kernels at K = F = 64, 4 coordinates, from the ncu capture
 # summarised in profiles/select_knn_and_accumulate_2events_full.md (traffic grows with the hits).
 ACC_DRAM_BYTES_PER_HIT = 1972
-KNN_DRAM_BYTES_PER_HIT = 409
-KNN_ISSUE_ACTIVE_PCT = 75.4
-KNN_WARP_INSTR_PER_QUERY = 5020
+KNN_DRAM_BYTES_PER_HIT = 438
+KNN_ISSUE_ACTIVE_PCT = 90.4
+KNN_WARP_INSTR_PER_QUERY = 5715
 
 
 def parse():
