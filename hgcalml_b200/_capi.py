@@ -41,6 +41,7 @@ def _load():
         "hgc_binned_select_knn_workspace_bytes": (S, [I, I, I, I]),
         "hgc_binned_select_knn": (I, [P] * 9 + [I] * 7 + [P, S, P]),
         "hgc_binned_select_knn_static": (I, [P] * 9 + [I] * 7 + [P]),
+        "hgc_binned_select_knn_static_status": (I, [P, ctypes.POINTER(ctypes.c_uint)]),
         "hgc_index_replacer": (I, [P, P, P, I, I, P, P]),
         "hgc_accumulate_knn": (I, [P] * 5 + [I] * 6 + [P]),
         "hgc_accumulate_knn_exp": (I, [P] * 5 + [I] * 5 + [ctypes.c_float, P, P]),
@@ -87,6 +88,12 @@ def ptr(t):
 
 
 def stream_of(t: torch.Tensor):
+    """The current stream of the tensor's device.  The library launches on the calling thread's
+    current device, so that device must be the tensor's."""
+    if t.device.index is not None and t.device.index != torch.cuda.current_device():
+        raise HgcError(f"tensors live on {t.device} but the current CUDA device is "
+                       f"cuda:{torch.cuda.current_device()}: call torch.cuda.set_device (or use "
+                       "torch.cuda.device) before calling hgcalml_b200 ops")
     return c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 

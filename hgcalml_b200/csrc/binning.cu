@@ -214,8 +214,10 @@ int compute_grid(const float *coords, int coord_stride, int n_dims, int n_all, i
 
 int range_partial_blocks(int n_vert)
 {
+    // a fixed cap (the workspace size depends on it, so it must not depend on the device)
+    constexpr int kMaxPartialBlocks = 296;
     int b = div_up(n_vert > 0 ? n_vert : 1, 256 * 8);
-    return b > 2 * kNumSMs ? 2 * kNumSMs : b;
+    return b > kMaxPartialBlocks ? kMaxPartialBlocks : b;
 }
 
 int launch_bin_keys(const float *coords, int coord_stride, int n_dims, const float *shift,

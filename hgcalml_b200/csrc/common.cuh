@@ -11,7 +11,6 @@ namespace hgc {
 
 constexpr int kWarp = 32;
 constexpr size_t kAlign = 256;
-constexpr int kNumSMs = 148;  // B200; only used to size persistent grids
 
 inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -46,6 +45,8 @@ void set_cuda_error(cudaError_t e);
     } while (0)
 
 void count_launch();
+// Multiprocessors of the calling thread's current device (asked for once per device); sizes persistent grids.
+int sm_count();
 #define HGC_LAUNCH_CHECK()                   \
     do {                                     \
         ::hgc::count_launch();               \

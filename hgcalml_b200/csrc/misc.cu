@@ -11,6 +11,20 @@ void set_cuda_error(cudaError_t e) { t_last_cuda_error = e; }
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+int sm_count()
+{
+    constexpr int kMaxDevices = 64, kDefault = 148;  // 148: B200, used only if the query fails
+    static std::atomic<int> cached[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kDefault;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kDefault;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
 namespace {
 
 // replaced[i] = replacements[to_be_replaced[i]]; negative entries pass through; entries beyond

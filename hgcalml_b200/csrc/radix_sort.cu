@@ -195,16 +195,20 @@ digit_scatter_kernel(const int *__restrict__ keys_in, const int *__restrict__ va
     }
 }
 
+// One thread per table entry: bounds[b] = number of keys below b = first position whose key is >= b
+// (keys are ascending; keys >= n_bins are sentinels that count for no bin).  A binary search per
+// entry costs log2(n) cached loads and no thread ever fills a run of empty bins by itself.
 __global__ void boundaries_kernel(const int *__restrict__ keys, int n, int *__restrict__ bounds,
                                   int n_bins)
 {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int k = min(keys[i], n_bins);
-    const int prev = i == 0 ? -1 : min(keys[i - 1], n_bins);
-    for (int b = prev + 1; b <= k; b++) bounds[b] = i;
-    if (i == n - 1)
-        for (int b = k + 1; b <= n_bins; b++) bounds[b] = n;
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b > n_bins) return;
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (keys[mid] < b) lo = mid + 1; else hi = mid;
+    }
+    bounds[b] = lo;
 }
 
 __global__ void fill_int_kernel(int *__restrict__ p, int n, int v)
@@ -276,7 +280,7 @@ int boundaries_from_sorted_keys(const int *sorted_keys, int n, int *bin_boundari
     if (n <= 0) {
         fill_int_kernel<<<div_up(n_bins + 1, 256), 256, 0, stream>>>(bin_boundaries, n_bins + 1, 0);
     } else {
-        boundaries_kernel<<<div_up(n, 256), 256, 0, stream>>>(sorted_keys, n, bin_boundaries, n_bins);
+        boundaries_kernel<<<div_up(n_bins + 1, 256), 256, 0, stream>>>(sorted_keys, n, bin_boundaries, n_bins);
     }
     HGC_LAUNCH_CHECK();
     return HGC_OK;

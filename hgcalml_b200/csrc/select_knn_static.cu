@@ -19,7 +19,8 @@ constexpr size_t kStaticBytes = hgc::kAlign + (size_t)kStaticMaxVert * sizeof(fl
 static __device__ __align__(256) unsigned char g_knn_scratch[kStaticBytes];
 
 // In host code `g_knn_scratch` is only a handle for the runtime, not a device address; the real
-// address is asked for once per device, with that device current, and remembered here.
+// address is asked for once per device, with that device current, and remembered here.  (It stays
+// valid for the life of the device's primary context, i.e. until a cudaDeviceReset.)
 std::mutex g_mutex;
 void *g_device_ptr[kMaxDevices] = {nullptr};
 
@@ -71,4 +72,16 @@ extern "C" int hgc_binned_select_knn_static(
                              d_bin_width, d_direction, d_indices, d_dist, nullptr, nullptr, n_vert,
                              n_neigh, n_bin_dim, n_bboundaries, tf_compat, use_direction != 0,
                              ws.status(), stream);
+}
+
+extern "C" int hgc_binned_select_knn_static_status(hgc_stream_t stream_, unsigned *status_out)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!status_out) return HGC_ERR_INVALID_ARGUMENT;
+    void *scratch = nullptr;
+    if (int rc = scratch_for_current_device(&scratch)) return rc;
+    // the status word is the first word of the scratch (Carver::status)
+    HGC_CUDA_TRY(cudaMemcpyAsync(status_out, scratch, sizeof(unsigned), cudaMemcpyDeviceToHost, stream));
+    HGC_CUDA_TRY(cudaStreamSynchronize(stream));
+    return *status_out ? HGC_ERR_DEVICE_STATUS : HGC_OK;
 }

@@ -18,7 +18,7 @@ from .binned_select_knn_op import BinnedSelectKnn
 
 class KnnAccumulatePipeline:
     def __init__(self, K: int, device, events_per_chunk: int = 2, distance_scale: float = 10.,
-                 n_slots: int = 2, with_max_idxs: bool = True):
+                 n_slots: int = 2, with_max_idxs: bool = False):
         self.K = int(K)
         self.device = torch.device(device)
         self.events_per_chunk = max(1, int(events_per_chunk))
@@ -44,13 +44,23 @@ class KnnAccumulatePipeline:
                 coords=torch.empty((max_hits, n_coords), dtype=torch.float32, device=self.device),
                 feats=torch.empty((max_hits, n_feat), dtype=torch.float32, device=self.device),
                 rs=torch.empty((max_events + 1,), dtype=torch.int32, device=self.device),
-                loaded=torch.cuda.Event(), consumed=torch.cuda.Event()))
+                coords_loaded=torch.cuda.Event(), loaded=torch.cuda.Event(), consumed=torch.cuda.Event()))
             self._slots[-1]["consumed"].record(torch.cuda.current_stream(self.device))
 
-    def run(self, coords: torch.Tensor, feats: torch.Tensor, row_splits, out: torch.Tensor):
+    def run(self, coords: torch.Tensor, feats: torch.Tensor, row_splits, out: torch.Tensor, wait: bool = True,
+            copies_only: bool = False):
         """coords [N,C], feats [N,F]: pinned host float32 tensors; row_splits: host int array [E+1];
-        out [N,2F]: pinned host float32 tensor that receives [mean | max].  Returns when all copies
-        into ``out`` have been enqueued and the D2H stream has been synchronised."""
+        out [N,2F]: pinned host float32 tensor that receives [mean | max].
+
+        With ``wait`` (the default) the call returns once every row of ``out`` has arrived in host
+        memory (the device-to-host stream is synchronised).  With ``wait=False`` it returns as soon
+        as the work is enqueued: the caller's current CUDA stream then waits for the three pipeline
+        streams, but the host does not, so ``out`` must not be read before that stream (or the
+        device) has been synchronised.
+
+        ``copies_only`` skips the two ops and moves the same bytes through the same buffers, streams
+        and events (the result rows are whatever the staging buffer holds): the transfer-only time of
+        the pipeline, against which the full call can be compared."""
         rs = np.asarray(row_splits, dtype=np.int64)
         n_events = len(rs) - 1
         chunks = [(e0, min(e0 + self.events_per_chunk, n_events))
@@ -76,16 +86,24 @@ class KnnAccumulatePipeline:
             n = hi - lo
             with torch.cuda.stream(self.s_h2d):
                 self.s_h2d.wait_event(slot["consumed"])
+                # coordinates and row splits first: the search can start while the (16 times larger)
+                # features of the same chunk are still on their way
                 slot["coords"][:n].copy_(coords[lo:hi], non_blocking=True)
-                slot["feats"][:n].copy_(feats[lo:hi], non_blocking=True)
                 slot["rs"][:e1 - e0 + 1].copy_(rs_chunks[c], non_blocking=True)
+                slot["coords_loaded"].record(self.s_h2d)
+                slot["feats"][:n].copy_(feats[lo:hi], non_blocking=True)
                 slot["loaded"].record(self.s_h2d)
             with torch.cuda.stream(self.s_run):
-                self.s_run.wait_event(slot["loaded"])
-                idx, d2, sorting = BinnedSelectKnn(self.K, slot["coords"][:n], slot["rs"][:e1 - e0 + 1],
-                                                   return_sorting=True)
-                res, _ = AccumulateKnn(d2, slot["feats"][:n], idx, order=sorting,
-                                       distance_scale=self.distance_scale, with_max_idxs=self.with_max_idxs)
+                self.s_run.wait_event(slot["coords_loaded"])
+                if copies_only:
+                    self.s_run.wait_event(slot["loaded"])
+                    res = torch.empty((n, 2 * feats.shape[1]), dtype=torch.float32, device=self.device)
+                else:
+                    idx, d2, sorting = BinnedSelectKnn(self.K, slot["coords"][:n], slot["rs"][:e1 - e0 + 1],
+                                                       return_sorting=True)
+                    self.s_run.wait_event(slot["loaded"])
+                    res, _ = AccumulateKnn(d2, slot["feats"][:n], idx, order=sorting,
+                                           distance_scale=self.distance_scale, with_max_idxs=self.with_max_idxs)
                 slot["consumed"].record(self.s_run)
                 done = torch.cuda.Event()
                 done.record(self.s_run)
@@ -98,4 +116,6 @@ class KnnAccumulatePipeline:
         start.wait_stream(self.s_d2h)
         start.wait_stream(self.s_run)
         start.wait_stream(self.s_h2d)
+        if wait:
+            self.s_d2h.synchronize()
         return out

@@ -7,7 +7,11 @@
 // tf.load_op_library.  A shim does shape checks, allocate_output / allocate_temp, and ONE call
 // into the library on the op's own CUDA stream; it never synchronises the device.
 //
-// Build (needs a TensorFlow installation; see INTEGRATION.md):
+// Written against the C++ op API of TensorFlow 2.10 - 2.15 (OkStatus(), OpKernelContext::allocate_temp
+// with a TensorShape, Tensor::flat<T>(), eigen_device<GPUDevice>().stream()); for 2.4 - 2.9 the one
+// difference, Status::OK() in place of OkStatus(), is selected from the version header below.
+//
+// Build (needs a TensorFlow installation):
 //   g++ -std=c++17 -shared -fPIC hgc_tf_ops.cc -o hgc_tf_ops.so \
 //       $(python -c 'import tensorflow as tf; print(" ".join(tf.sysconfig.get_compile_flags()))') \
 //       -I../../include -L.. -lhgcalml_b200 \
@@ -16,6 +20,7 @@
 #include "tensorflow/core/framework/op.h"
 #include "tensorflow/core/framework/op_kernel.h"
 #include "tensorflow/core/framework/shape_inference.h"
+#include "tensorflow/core/public/version.h"
 
 #include "hgcalml_b200.h"
 
@@ -27,6 +32,10 @@ typedef Eigen::GpuDevice GPUDevice;
 inline hgc_stream_t StreamOf(OpKernelContext *ctx) {
     return static_cast<hgc_stream_t>(ctx->eigen_device<GPUDevice>().stream());
 }
+
+#if TF_MAJOR_VERSION < 2 || (TF_MAJOR_VERSION == 2 && TF_MINOR_VERSION < 10)
+inline Status OkStatus() { return Status::OK(); }
+#endif
 
 inline Status FromHgc(int rc, const char *op) {
     if (rc == HGC_OK) return OkStatus();
@@ -73,7 +82,7 @@ public:
         OP_REQUIRES_OK(ctx, ctx->allocate_output(2, {total}, &nper));
         // the kernels read nbins / bin_width on the device: stage the few host values in a temp
         Tensor dev_params;
-        OP_REQUIRES_OK(ctx, ctx->allocate_temp(DT_INT32, {n_coords + 1}, &dev_params));
+        OP_REQUIRES_OK(ctx, ctx->allocate_temp(DT_INT32, TensorShape({(int64_t)n_coords + 1}), &dev_params));
         int *d_nbins = dev_params.flat<int>().data();
         float *d_bw = reinterpret_cast<float *>(d_nbins + n_coords);
         auto stream = ctx->eigen_device<GPUDevice>().stream();

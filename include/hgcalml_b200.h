@@ -9,14 +9,17 @@
  *    (`workspace`, sized by the matching *_workspace_bytes query; 256-byte aligned).
  *  - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call
  *    synchronises the device and no call touches the legacy default stream unless the
- *    caller passes it.  Two entries wait for their own stream and say so:
- *    hgc_workspace_status and hgc_build_and_assign_condensates.
+ *    caller passes it.  The device that owns `stream` and the d_ pointers must be the calling
+ *    thread's current device (cudaSetDevice) when an entry is called.  The entries that wait
+ *    for their own stream say so: hgc_workspace_status, hgc_binned_select_knn_static_status and
+ *    hgc_build_and_assign_condensates.
  *  - Return value: HGC_OK or a negative HGC_ERR_* code.  Nothing throws, nothing prints.
  *    Problems that only the device can see (an index outside its table, a bin outside the
  *    grid, an iteration cap reached) set a status word in the workspace, which
  *    hgc_workspace_status() reads back.
  *  - Re-entrant: the only global state is a statistics counter of kernel launches; concurrent
- *    calls need distinct workspaces.
+ *    calls need distinct workspaces.  The one exception is hgc_binned_select_knn_static, whose
+ *    scratch is a per-device array inside the library (see there).
  *
  * The paths named in the comments are relative to the cms-pepr/HGCalML repository.
  */
@@ -84,6 +87,12 @@ int hgc_bin_by_coordinates(
  * reference leaves them in scan order; as a set the rows are identical -- padded with -1
  * (or the query's own index when tf_compat) and distance 0.
  * Limits: 2 <= n_bin_dim <= 5, 2 <= n_coords <= 16, 1 <= n_neigh <= 513.
+ * Precondition beyond the reference's: d_dim_bin_idx and d_bin_width must be the bins of the
+ * leading n_bin_dim columns of d_coord (up to a common shift of the coordinates), which is what
+ * BinByCoordinates produces.  From the second shell of bins on, the search leaves out bins whose
+ * index distance from the query's bin already puts them beyond the current K-th best; the
+ * reference scans every bin of a shell and so tolerates bins that do not match the coordinates.
+ * A build with -DHGC_KNN_BINPRUNE=0 scans the reference's full candidate set.
  * ------------------------------------------------------------------------------------- */
 size_t hgc_binned_select_knn_workspace_bytes(int n_vert, int n_neigh, int n_coords, int n_bin_dim);
 int hgc_binned_select_knn(
@@ -111,9 +120,19 @@ int hgc_binned_select_knn(
  * HGC_ERR_STATIC_SCRATCH_TOO_SMALL is returned and nothing is launched.
  * First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that
  * device current) and remembers it; make that first call outside any stream capture.
+ * The remembered address belongs to the device's current primary context: after a
+ * cudaDeviceReset it is stale, so a process that resets a device must not call this entry on that
+ * device again.  The scratch is chosen by the calling thread's current device, which must be the
+ * device of `stream` and of the d_ pointers.
  * Sharing: all calls on one device use the same array, which still holds the previous call's
  * data; the entry rewrites what it reads and clears the status word itself, but two calls that
  * overlap on the GPU (different streams, or different host threads) race on it -- serialise them.
+ * The same precondition on d_dim_bin_idx / d_bin_width as for hgc_binned_select_knn applies.
+ *
+ * hgc_binned_select_knn_static_status is this entry's hgc_workspace_status: it copies the status
+ * word that the last hgc_binned_select_knn_static call on the current device left in the built-in
+ * scratch to *status_out (host memory), waits for `stream`, and returns HGC_ERR_DEVICE_STATUS when
+ * the word is non-zero.  It allocates nothing either.
  * ------------------------------------------------------------------------------------- */
 #define HGC_STATIC_KNN_MAX_VERT   262144
 #define HGC_STATIC_KNN_MAX_COORDS 4
@@ -123,6 +142,7 @@ int hgc_binned_select_knn_static(
         int *d_indices, float *d_dist,
         int n_vert, int n_neigh, int n_coords, int n_bin_dim, int n_bboundaries,
         int tf_compat, int use_direction, hgc_stream_t stream);
+int hgc_binned_select_knn_static_status(hgc_stream_t stream, unsigned *status_out);
 
 /* ---------------------------------------------------------------------------------------
  * IndexReplacer -- replaces IndexReplacerOpFunctor (modules/compiled/index_replacer_kernel.h:8-20):

@@ -27,6 +27,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _PORT_SO = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libref.so")
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libref_cuda.so")
 
 _fp = POINTER(c_float)
 _ip = POINTER(c_int)
@@ -193,6 +194,32 @@ def op_select_knn_grad(grad_dist, indices, coords):
     lib("port").fn("select_knn_grad")(_f(grad_dist), _i(indices), _f(coords), _f(out),
                                       c_int(n), c_int(k), c_int(coords.shape[1]))
     return out
+
+
+def have_ref_cuda() -> bool:
+    """True where the reference's GPU kernels of SelectKnnGrad were compiled (oracle/Makefile)."""
+    return os.path.exists(_REF_CUDA_SO)
+
+
+def op_select_knn_grad_ref_cuda(grad_dist, indices, dist, coords):
+    """The reference's own GPU functor for SelectKnnGrad (select_knn_grad_kernel.cu.cc:81-216), its
+    only implementation of the op, run on the current CUDA device; torch holds the device memory.
+    The kernels scatter with float atomicAdd, so the result is reproducible only up to summation
+    order.  Returns grad_coords [N,C] as a numpy array."""
+    import torch
+    dll = ctypes.CDLL(_REF_CUDA_SO)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    t = [torch.as_tensor(_c32f(grad_dist), device=dev), torch.as_tensor(_c32i(indices), device=dev),
+         torch.as_tensor(_c32f(dist), device=dev), torch.as_tensor(_c32f(coords), device=dev)]
+    out = torch.zeros_like(t[3])
+    torch.cuda.synchronize()  # the functor runs on the legacy default stream
+    n, k = indices.shape
+    rc = dll.ref_cuda_select_knn_grad(*[ctypes.c_void_p(x.data_ptr()) for x in t], ctypes.c_void_p(out.data_ptr()),
+                                      c_int(n), c_int(k), c_int(coords.shape[1]))
+    torch.cuda.synchronize()
+    if rc != 0:
+        raise RuntimeError(f"reference SelectKnnGrad kernels failed with CUDA error {rc}")
+    return out.cpu().numpy()
 
 
 def op_local_distance(coords, neigh_idxs, backend="port"):

@@ -1,3 +1,5 @@
+import functools
+import inspect
 import os
 import sys
 
@@ -26,12 +28,34 @@ def load_golden(name):
     return g
 
 
+class _Checker:
+    """The checker module with a default back end: every routine that takes ``backend=`` gets the
+    compiled reference (``oracle/_ref/libref.so``) where that library is present, else the plain-C
+    restatement; a test that names a back end itself keeps it."""
+
+    def __init__(self, module, backend):
+        self._module = module
+        self.backend = backend
+
+    def __getattr__(self, name):
+        attr = getattr(self._module, name)
+        if callable(attr):
+            try:
+                takes_backend = "backend" in inspect.signature(attr).parameters
+            except (TypeError, ValueError):
+                takes_backend = False
+            if takes_backend:
+                return functools.partial(attr, backend=self.backend)
+        return attr
+
+
 @pytest.fixture(scope="session")
 def oracle():
-    """The CPU checker (plain-C restatement); built on first use."""
+    """The CPU checker: the reference's own compiled CPU kernels where they were built, else the
+    plain-C restatement (built on first use)."""
     from oracle import oracle as O
     O.lib("port")
-    return O
+    return _Checker(O, "ref" if O.have("ref") else "port")
 
 
 @pytest.fixture(scope="session")

@@ -5,7 +5,8 @@ builds oracle/_ref/libref.so from it).  The op arithmetic in the stored outputs 
 compiled code; only the TensorFlow glue of its Python wrappers is restated in numpy
 (oracle/oracle.py).  Inputs are seeded synthetic data.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # every fixture
+    python tests/golden/make_golden.py siblings   # only the LocalDistance / PushKnn / IndexReplacer fixture
 """
 import os
 import sys
@@ -30,8 +31,31 @@ def knn_case(name, K, coords, feats, row_splits, **kw):
     print(name, coords.shape, "K", K, "rows with padding", int((idx < 0).any(axis=1).sum()))
 
 
+def sibling_cases():
+    """LocalDistance, PushKnn, PushKnnGrad and IndexReplacer on the neighbour rows of a golden kNN case
+    (rows with -1 padding included)."""
+    base = "knn_showers4d"
+    case = dict(np.load(os.path.join(OUT, base + ".npz")))
+    idx, feats, coords = case["idx"], case["feats"], case["coords"]
+    rng = np.random.default_rng(13)
+    w = np.exp(-(np.float32(10.) * case["dist"])).astype(np.float32)
+    local_dist = O.op_local_distance(coords, idx, backend=BACKEND)
+    pushed = O.op_push_knn(w, feats, idx, backend=BACKEND)
+    grad = rng.standard_normal(feats.shape, dtype=np.float32)
+    push_wgrad, push_fgrad = O.op_push_knn_grad(grad, w, feats, idx, backend=BACKEND)
+    replacements = rng.permutation(idx.shape[0]).astype(np.int32)
+    replaced = O.op_index_replacer(idx, replacements, backend=BACKEND)
+    np.savez_compressed(os.path.join(OUT, "sibling_ops_showers4d.npz"), base=np.array(base),  # weights = exp(-10 dist)
+                        local_dist=local_dist, pushed=pushed, push_grad_in=grad, push_wgrad=push_wgrad,
+                        push_fgrad=push_fgrad, replacements=replacements, replaced=replaced)
+    print("sibling ops", local_dist.shape, pushed.shape, push_wgrad.shape, replaced.shape)
+
+
 def main():
     assert O.have("ref"), "build oracle/_ref/libref.so first (make -C oracle ref)"
+    if sys.argv[1:] == ["siblings"]:
+        sibling_cases()
+        return
     # uniform 3-D event, explicit number of bins (small sibling of the 20k-hit CPU configuration)
     c, f, rs = synth.uniform_event(1500, 3, 8, seed=101)
     knn_case("knn_uniform3d", 16, c, f, rs, n_bins=5)
@@ -87,6 +111,8 @@ def main():
         np.savez_compressed(os.path.join(OUT, "gravnet_collect_" + base[4:] + ".npz"), base=np.array(base),
                             collected=collected)
         print("gravnet_collect", base, collected.shape)
+
+    sibling_cases()
 
     # bin_by_coordinates op outputs
     c, _, rs = synth.shower_batch([400, 0, 650], dims=3, n_feat=1, seed=77)

@@ -333,11 +333,17 @@ def test_host_pipeline_matches_direct_calls(cuda):
     pipe = KnnAccumulatePipeline(K, cuda, events_per_chunk=2, distance_scale=10.)
     for _ in range(2):  # second run reuses the device slots
         out.zero_()
-        pipe.run(cp, fp, rs, out)
-        torch.cuda.synchronize()
+        pipe.run(cp, fp, rs, out)   # returns with every row of `out` in host memory: no synchronise here
+        got = out.clone()
         idx, d2 = BinnedSelectKnn(K, T(c, cuda), T(rs, cuda))
         ref, _ = AccumulateKnn(d2, T(f, cuda), idx, distance_scale=10.)
-        assert torch.equal(out, ref.cpu())
+        assert torch.equal(got, ref.cpu())
+    # stream-ordered variant: the caller synchronises; the copies-only mode runs the same transfers
+    out.zero_()
+    pipe.run(cp, fp, rs, out, wait=False)
+    torch.cuda.synchronize()
+    assert torch.equal(out, got)
+    pipe.run(cp, fp, rs, out, copies_only=True)
 
 
 # ------------------------------------------------------------------ backward ops
@@ -379,6 +385,32 @@ def test_select_knn_grad_vs_checker(cuda, oracle):
     ref = oracle.op_select_knn_grad(gd, g["idx"], g["coords"])
     got = SelectKnnGrad(T(gd, cuda), T(g["idx"], cuda), T(g["dist"], cuda), T(g["coords"], cuda))
     assert np.array_equal(bits(N(got)), bits(ref))
+
+
+@pytest.mark.parametrize("name", ["knn_showers4d", "knn_showers4d_tfcompat", "knn_uniform3d"])
+def test_select_knn_grad_vs_reference_gpu_kernels(cuda, name):
+    """The pin for SelectKnnGrad: the reference implements the op on the GPU only
+    (select_knn_grad_kernel.cu.cc:81-216; the CPU functor is empty), so its own kernels, compiled
+    with nvcc, are the oracle here.  They scatter with float atomicAdd in no fixed order, the
+    library sums in (hit, slot) order: 1e-5 relative to the summed terms."""
+    from oracle import oracle as O
+    if not O.have_ref_cuda():
+        pytest.skip("oracle/_ref/libref_cuda.so was not built (no reference checkout at build time)")
+    from hgcalml_b200.binned_select_knn_op import SelectKnnGrad
+    g = load_golden(name)
+    idx, c = g["idx"], g["coords"]
+    gd = np.random.default_rng(5).standard_normal(idx.shape).astype(np.float32)
+    ref = O.op_select_knn_grad_ref_cuda(gd, idx, g["dist"], c)
+    got = N(SelectKnnGrad(T(gd, cuda), T(idx, cuda), T(g["dist"], cuda), T(c, cuda)))
+    # size of the summed terms per output element: sum over the edges that touch hit i of |2 g (x_m - x_i)|
+    terms = np.zeros(c.shape, np.float64)
+    for k in range(idx.shape[1]):
+        m = idx[:, k]
+        ok = m >= 0
+        t = np.abs(2.0 * gd[ok, k][:, None] * (c[m[ok]].astype(np.float64) - c[ok]))
+        np.add.at(terms, np.nonzero(ok)[0], t)
+        np.add.at(terms, m[ok], t)
+    assert (np.abs(got - ref) <= 1e-5 * np.maximum(terms, np.abs(ref)) + 1e-12).all()
 
 
 def test_autograd_through_the_neighbour_path(cuda):

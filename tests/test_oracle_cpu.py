@@ -117,7 +117,8 @@ ACCGRAD_CASES = [f"accgrad_{t}_{m}" for t in ("tfcompat", "padded") for m in ("m
 @pytest.mark.parametrize("name", ACCGRAD_CASES)
 def test_port_matches_golden_accumulate_grad(oracle, name):
     g = load_golden(name)
-    gw, gf = oracle.op_accumulate_knn_grad(g["grad_out"], g["weights"], g["feats"], g["idx"], g["maxidx"])
+    gw, gf = oracle.op_accumulate_knn_grad(g["grad_out"], g["weights"], g["feats"], g["idx"], g["maxidx"],
+                                           backend="port")
     assert np.array_equal(bits(gw), bits(g["grad_weights"]))
     assert np.array_equal(bits(gf), bits(g["grad_feats"]))
 
@@ -205,3 +206,66 @@ def test_gravnet_layer_restatements_shapes(oracle):
           [rng.standard_normal((8, 5), dtype=np.float32), rng.standard_normal(5, dtype=np.float32)]]
     mp = oracle.DistanceWeightedMessagePassing(f, idx[:, 1:], dist[:, 1:], wm)
     assert mp.shape == (750, 2 * (4 + 5) + 10) and np.array_equal(mp[:, 18:], f)
+
+
+def _sibling_inputs():
+    g = load_golden("sibling_ops_showers4d")
+    base = load_golden("knn_showers4d")
+    w = np.exp(-(np.float32(10.) * base["dist"])).astype(np.float32)
+    return g, base, w
+
+
+def test_port_matches_golden_sibling_ops(oracle):
+    """LocalDistance, PushKnn, PushKnnGrad and IndexReplacer: the plain-C restatement against vectors
+    produced by the reference's compiled CPU kernels (local_distance_kernel.cc:47-70,
+    push_knn_kernel.cc:35-71, push_knn_grad_kernel.cc:22-95, index_replacer_kernel.cc:28-49)."""
+    g, base, w = _sibling_inputs()
+    assert np.array_equal(bits(oracle.op_local_distance(base["coords"], base["idx"], backend="port")),
+                          bits(g["local_dist"]))
+    assert np.array_equal(bits(oracle.op_push_knn(w, base["feats"], base["idx"], backend="port")), bits(g["pushed"]))
+    wg, fg = oracle.op_push_knn_grad(g["push_grad_in"], w, base["feats"], base["idx"], backend="port")
+    assert np.array_equal(bits(wg), bits(g["push_wgrad"])) and np.array_equal(bits(fg), bits(g["push_fgrad"]))
+    assert np.array_equal(oracle.op_index_replacer(base["idx"], g["replacements"], backend="port"), g["replaced"])
+
+
+@pytest.mark.skipif("not __import__('oracle.oracle').oracle.have('ref')")
+@pytest.mark.parametrize("seed", [7, 8])
+def test_port_matches_compiled_reference_sibling_and_backward_ops(oracle, seed):
+    """Fresh inputs: restatement against the compiled reference for the ops beside the main path."""
+    rng = np.random.default_rng(seed)
+    c, f, rs = synth.shower_batch([int(x) for x in rng.integers(1, 1500, 3)], dims=3 + seed % 2, n_feat=9,
+                                  seed=2000 + seed)
+    idx, dist = oracle.BinnedSelectKnn(13, c, rs, backend="ref")
+    w = np.exp(-dist).astype(np.float32)
+    a, b = (oracle.op_local_distance(c, idx, backend=k) for k in ("port", "ref"))
+    assert np.array_equal(bits(a), bits(b))
+    a, b = (oracle.op_push_knn(w, f, idx, backend=k) for k in ("port", "ref"))
+    assert np.array_equal(bits(a), bits(b))
+    grad = rng.standard_normal(f.shape, dtype=np.float32)
+    a, b = (oracle.op_push_knn_grad(grad, w, f, idx, backend=k) for k in ("port", "ref"))
+    assert np.array_equal(bits(a[0]), bits(b[0])) and np.array_equal(bits(a[1]), bits(b[1]))
+    rep = rng.permutation(idx.shape[0]).astype(np.int32)
+    assert np.array_equal(oracle.op_index_replacer(idx, rep, backend="port"),
+                          oracle.op_index_replacer(idx, rep, backend="ref"))
+    for mm in (True, False):
+        out, maxidx = oracle.op_accumulate_knn(w, f, idx, mean_and_max=mm, backend="ref")
+        gout = rng.standard_normal(out.shape, dtype=np.float32)
+        a, b = (oracle.op_accumulate_knn_grad(gout, w, f, idx, maxidx, backend=k) for k in ("port", "ref"))
+        assert np.array_equal(bits(a[0]), bits(b[0])) and np.array_equal(bits(a[1]), bits(b[1]))
+
+
+@pytest.mark.skipif("not __import__('oracle.oracle').oracle.have('ref')")
+def test_port_matches_compiled_reference_at_full_event_size(oracle):
+    """One 200k-hit event, K = 64, F = 64 (the size of the benchmark's events): restatement and compiled
+    reference agree bit for bit, slot order included, on the search and on AccumulateKnn."""
+    n, K = 200000, 64
+    c = synth.shower_event(n, dims=4, seed=500)
+    rs = np.array([0, n], np.int32)
+    a = oracle.BinnedSelectKnn(K, c, rs, backend="port")
+    b = oracle.BinnedSelectKnn(K, c, rs, backend="ref")
+    assert np.array_equal(a[0], b[0]) and np.array_equal(bits(a[1]), bits(b[1]))
+    f = np.random.default_rng(3).standard_normal((n, 64), dtype=np.float32)
+    rows = slice(0, 40000)   # AccumulateKnn rows are independent: a fifth of the event keeps the suite short
+    x = oracle.op_accumulate_knn_rows(np.exp(-np.float32(10.) * b[1]).astype(np.float32), f, b[0], 0, 40000, backend="port")
+    y = oracle.op_accumulate_knn_rows(np.exp(-np.float32(10.) * b[1]).astype(np.float32), f, b[0], 0, 40000, backend="ref")
+    assert np.array_equal(bits(x[0]), bits(y[0])) and np.array_equal(x[1], y[1])
