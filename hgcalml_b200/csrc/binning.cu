@@ -129,20 +129,38 @@ range_partial_kernel(const float *__restrict__ coords, int coord_stride, int n_d
     }
 }
 
+constexpr int kGridSetupThreads = 256;
+
 // One block: finishes the min/max reduction and derives the grid exactly as the Python wrappers do
 // (modules/bin_by_coordinates_op.py:49-71, modules/binned_select_knn_op.py:57-63), in float32.
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kGridSetupThreads)
 grid_setup_kernel(const float *__restrict__ partial, int n_partials, int n_dims, int n_all,
                   const int *__restrict__ row_splits, int n_rs, int n_bins_arg, int n_neigh,
                   int pre_normalized, GridParams *__restrict__ g)
 {
+    // min / max over the per-block partial results: thread t looks at coordinate t % 8 of every
+    // (kGridSetupThreads / 8)-th partial, a shared-memory pass combines the threads of a coordinate
+    static_assert(kMaxBinDims == 8 && kGridSetupThreads % 8 == 0, "layout of the reduction");
+    __shared__ float s_mn[kGridSetupThreads], s_mx[kGridSetupThreads];
+    {
+        const int cc = threadIdx.x & 7;
+        float a = INFINITY, b = -INFINITY;
+        for (int p = threadIdx.x >> 3; p < n_partials; p += kGridSetupThreads / 8) {
+            a = fminf(a, partial[((size_t)p * 2 + 0) * kMaxBinDims + cc]);
+            b = fmaxf(b, partial[((size_t)p * 2 + 1) * kMaxBinDims + cc]);
+        }
+        s_mn[threadIdx.x] = a;
+        s_mx[threadIdx.x] = b;
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;  // the rest is one warp's work
     const int c = threadIdx.x;
     float mn = 0.f, mx = 0.f;
     if (c < n_all) {
         mn = INFINITY; mx = -INFINITY;
-        for (int p = 0; p < n_partials; p++) {
-            mn = fminf(mn, partial[((size_t)p * 2 + 0) * kMaxBinDims + c]);
-            mx = fmaxf(mx, partial[((size_t)p * 2 + 1) * kMaxBinDims + c]);
+        for (int t = c; t < kGridSetupThreads; t += 8) {
+            mn = fminf(mn, s_mn[t]);
+            mx = fmaxf(mx, s_mx[t]);
         }
     }
     // The wrapper shifts by the minimum first; x -> x - mn is monotone, so the shifted extremes
@@ -206,7 +224,7 @@ int compute_grid(const float *coords, int coord_stride, int n_dims, int n_all, i
     const int blocks = range_partial_blocks(n_vert);
     range_partial_kernel<<<blocks, 256, 0, stream>>>(coords, coord_stride, n_all, n_vert, partial);
     HGC_LAUNCH_CHECK();
-    grid_setup_kernel<<<1, 32, 0, stream>>>(partial, blocks, n_dims, n_all, row_splits, n_rs, n_bins_arg,
+    grid_setup_kernel<<<1, kGridSetupThreads, 0, stream>>>(partial, blocks, n_dims, n_all, row_splits, n_rs, n_bins_arg,
                                            n_neigh, pre_normalized, grid);
     HGC_LAUNCH_CHECK();
     return HGC_OK;

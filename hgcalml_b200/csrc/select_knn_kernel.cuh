@@ -61,11 +61,6 @@ static_assert(HGC_KNN_FLUSH_AT >= 1 && HGC_KNN_FLUSH_AT <= 32,
 #ifndef HGC_KNN_MIN_BLOCKS
 #define HGC_KNN_MIN_BLOCKS 8
 #endif
-// Consecutive queries a block takes from the global counter at a time (0: every warp draws its
-// queries straight from the global counter).
-#ifndef HGC_KNN_BLOCK_RUN
-#define HGC_KNN_BLOCK_RUN 0
-#endif
 constexpr int kKnnWarps = 8;
 constexpr int kKnnThreads = kKnnWarps * kWarp;
 
@@ -330,49 +325,19 @@ __global__ void __launch_bounds__(kKnnThreads, HGC_KNN_MIN_BLOCKS) select_knn_ke
     }
     const int bins_per_event = stride[0] * nb[0];
 
-    // Work distribution.  Queries differ a lot in cost (dense shower vs sparse noise), so nothing is
-    // assigned statically: a block takes a run of HGC_KNN_BLOCK_RUN consecutive bin-sorted queries
-    // from the global counter and its warps draw single queries of that run from a shared counter.
-    // The warps of a block therefore work on neighbouring queries at any time and find each
-    // other's candidate chunks and boxes in L1.
-#if HGC_KNN_BLOCK_RUN > 0
-    // (first query of the block's run) << 16 | queries of the run handed out so far
-    __shared__ unsigned long long s_run;
-    if (threadIdx.x == 0) s_run = (unsigned long long)HGC_KNN_BLOCK_RUN;  // "used up": the first taker refills
-    __syncthreads();
-#endif
+    // Warps fetch queries one at a time from one global counter: queries differ a lot in cost (dense
+    // shower vs sparse noise), and a fixed assignment leaves warps idle at the end of a block.  The
+    // counter also spreads neighbouring queries over all SMs, so that every SM always holds a mix of
+    // issue-bound (dense) and latency-bound (sparse) searches; giving a block runs of 16..256
+    // consecutive queries instead, so that its warps share candidate chunks in L1, was measured 25-35 %
+    // slower on the 200k-hit events.
     for (;;) {
     {
-#if HGC_KNN_BLOCK_RUN > 0
-    int run_begin = a.n_vert;
-    if (lane == 0) {
-        // No barrier anywhere: the warp that takes ticket number RUN fetches the block's next run
-        // from the global counter and publishes it; warps with a later ticket wait for that (a few
-        // hundred cycles; the wait is bounded, after which the warp fetches one query for itself).
-        for (int spin = 0;; spin++) {
-            const unsigned long long t = atomicAdd(&s_run, 1ull);
-            const unsigned taken = (unsigned)(t & 0xffffull);
-            if (taken < (unsigned)HGC_KNN_BLOCK_RUN) { run_begin = (int)(t >> 16) + (int)taken; break; }
-            if (taken == (unsigned)HGC_KNN_BLOCK_RUN) {
-                const unsigned nb = atomicAdd(a.work_counter, (unsigned)HGC_KNN_BLOCK_RUN);
-                atomicExch(&s_run, ((unsigned long long)nb << 16) | 1ull);
-                run_begin = (int)nb;
-                break;
-            }
-            if (taken > 0xff00u || spin > 4096) { run_begin = (int)atomicAdd(a.work_counter, 1u); break; }
-            __nanosleep(64);
-        }
-    }
-    run_begin = __shfl_sync(0xffffffffu, run_begin, 0);
-    if (run_begin >= a.n_vert) break;
-    const int run_end = run_begin + 1;
-#else
     int run_begin = 0;
     if (lane == 0) run_begin = (int)atomicAdd(a.work_counter, (unsigned)a.fetch);
     run_begin = __shfl_sync(0xffffffffu, run_begin, 0);
     if (run_begin >= a.n_vert) break;
     const int run_end = min(run_begin + a.fetch, a.n_vert);
-#endif
     for (int i = run_begin; i < run_end; i++) {
         const int out_row = a.row_map ? a.row_map[i] : i;
         const int self_id = a.id_map ? a.id_map[i] : i;
