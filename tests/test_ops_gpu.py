@@ -188,6 +188,29 @@ def test_accumulate_knn_vs_checker(cuda, oracle, n, K, F, mm):
         assert np.array_equal(N(ga), ra)
 
 
+@pytest.mark.parametrize("K,F", [(64, 64), (64, 48), (16, 32), (24, 16), (40, 128)])
+def test_accumulate_knn_ties_and_zeros(cuda, oracle, K, F):
+    """Rows without padding (the kernel's test-free path) whose products tie exactly: rectified features
+    (many zeros), repeated neighbour ids, equal weights, columns that are negative throughout.  The
+    maximum and the arg-max must follow the reference's rule -- the LAST slot whose product is >= the
+    running maximum wins (accumulate_knn_kernel.cc:65) -- bit for bit, and the mean its slot order."""
+    from hgcalml_b200.accknn_op import AccumulateLinKnn
+    rng = np.random.default_rng(1000 + K + F)
+    n = 3000
+    feat = np.maximum(rng.standard_normal((n, F), dtype=np.float32), 0)       # about half the entries are 0
+    feat[:, ::5] = -np.abs(rng.standard_normal((n, (F + 4) // 5), dtype=np.float32)) - 0.5   # negative columns
+    feat[:, 1::7] = 0.                                                          # all-zero columns
+    idx = rng.integers(0, n, (n, K)).astype(np.int32)
+    idx[:, 0] = np.arange(n)
+    idx[:, K // 2:] = idx[:, :K - K // 2]                                       # every neighbour appears twice
+    w = rng.integers(1, 4, (n, K)).astype(np.float32) / 4                       # few distinct weights
+    w[:, K // 2:] = w[:, :K - K // 2]
+    ro, ra = oracle.op_accumulate_knn(w, feat, idx)
+    go, ga = AccumulateLinKnn(T(w, cuda), T(feat, cuda), T(idx, cuda))
+    assert np.array_equal(bits(N(go)), bits(ro))
+    assert np.array_equal(N(ga), ra)
+
+
 def exp_weighted_tolerance(d, feats, idx, ref, rows_per_block=4096):
     """1e-5 relative, measured against the size of the summed terms: the mean may cancel to
     something much smaller than its terms, and the weights differ in their last bits (expf on the
