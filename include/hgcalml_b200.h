@@ -160,7 +160,13 @@ int hgc_index_replacer(
  * d_feat [n_vert, n_feat]; d_idxs [n_vert, n_neigh] (-1 = skip).  d_out_feat [n_vert, n_out_feat]
  * with n_out_feat = 2*n_feat ([mean | max]) when mean_and_max, else n_feat; d_out_maxidxs
  * [n_vert, n_feat] (written only when mean_and_max; may be NULL to skip it).
- * No workspace.  Sums run over the slots in order, so the mean is bit-identical to the CPU op.
+ * No workspace.  Sums run over the slots in order, so the mean is bit-identical to the CPU op;
+ * the max and its index follow the op's rule (the last slot whose product is >= the running
+ * maximum wins, accumulate_knn_kernel.cc:65).  Two corners differ from the CPU loop: a NaN product
+ * is ignored by the maximum (the CPU op keeps one that sits in slot 0), and when the maximum is a
+ * zero reached by products of both signs its sign bit may differ (+0 here, the later product's
+ * there); neither occurs with finite, non-negative weights and features without NaN and -0.
+ * Without d_out_maxidxs the arg-max bookkeeping is not run at all (about a third faster).
  * ------------------------------------------------------------------------------------- */
 int hgc_accumulate_knn(
         const float *d_weights, const float *d_feat, const int *d_idxs,
