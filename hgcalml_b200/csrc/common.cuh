@@ -74,11 +74,13 @@ __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 // Stable LSD radix sort of (key, value) pairs on keys in [0, 2^key_bits).  No atomics: per-warp
 // digit counters combined by scans, so the result is deterministic.  values_in == nullptr means
 // value i = i.  Sorted data ends up in keys_out / vals_out; keys_tmp / vals_tmp are ping-pong
-// buffers of n ints each, block_hist has sort_hist_ints(n) ints.
+// buffers of n ints each, block_hist has sort_hist_ints(n) ints.  With n_dev (device memory) the
+// number of items is min(n, *n_dev): n then only sizes the launches and the tables, so that a count
+// produced on the device needs no round trip to the host.
 size_t sort_hist_ints(int n);
 int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_out,
                int *keys_tmp, int *vals_tmp, int *block_hist, int n, int key_bits,
-               cudaStream_t stream);
+               cudaStream_t stream, const int *n_dev = nullptr);
 
 // Exclusive prefix sum of `len` ints in place; tile_sums needs scan_scratch_ints(len) ints.
 size_t scan_scratch_ints(int len);

@@ -47,10 +47,12 @@ __device__ __forceinline__ unsigned ordered_bits(float f)
 // tests no_condensation_mask_h at index 0 or 1 only, binned_assign_to_condensates_kernel.cc:193),
 // else 1 + descending beta.
 __global__ void priority_keys_kernel(const float *__restrict__ beta_h, const int *__restrict__ mask_h,
-                                     const int *__restrict__ row_splits_h, int num_rows, int n_h,
+                                     const int *__restrict__ row_splits_h, int num_rows, int n_h_max,
+                                     const int *__restrict__ n_h_dev,
                                      int *__restrict__ beta_keys, int *__restrict__ event_keys)
 {
     const int a = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n_h = n_h_dev ? min(n_h_max, *n_h_dev) : n_h_max;
     if (a >= n_h) return;
     const bool flagged = mask_h[a > 0 ? 1 : 0] != 0;  // n_h >= 2 whenever a > 0
     unsigned key = 0u;
@@ -68,9 +70,10 @@ __global__ void priority_keys_kernel(const float *__restrict__ beta_h, const int
 }
 
 __global__ void gather_int_kernel(const int *__restrict__ src, const int *__restrict__ idx,
-                                  int *__restrict__ dst, int n)
+                                  int *__restrict__ dst, int n_max, const int *__restrict__ n_dev)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = n_dev ? min(n_max, *n_dev) : n_max;
     if (i < n) dst[i] = src[idx[i]];
 }
 
@@ -471,7 +474,10 @@ extern "C" size_t hgc_binned_assign_to_condensates_workspace_bytes(int n_vert, i
     return w.s.used;
 }
 
-extern "C" int hgc_binned_assign_to_condensates(
+namespace hgc {
+// The op with the number of high-beta hits either exact on the host (d_n_vert_h == nullptr) or in
+// device memory (then n_vert_h is an upper bound that sizes workspace and launches).
+int assign_to_condensates(
         int dimensions, int dimensions_binning,
         const float *d_ccoords_h, const float *d_dist_h, const float *d_beta_h,
         const int *d_no_condensation_mask_h,
@@ -481,8 +487,8 @@ extern "C" int hgc_binned_assign_to_condensates(
         const int *d_indices_to_filtered,
         int *d_assignment, int *d_association, int *d_n_condensates, int *d_alpha_indices,
         const int *d_bin_splits, const int *d_n_bins, const float *d_bin_widths,
-        const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, int assign_by_max_beta,
-        void *workspace, size_t workspace_bytes, hgc_stream_t stream_)
+        const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, const int *d_n_vert_h,
+        int assign_by_max_beta, void *workspace, size_t workspace_bytes, hgc_stream_t stream_)
 {
     (void)dimensions_binning; (void)d_dist; (void)d_bin_splits; (void)d_n_bins; (void)d_bin_widths;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -512,13 +518,13 @@ extern "C" int hgc_binned_assign_to_condensates(
     if (n_vert_h > 0 && num_rows > 0) {
         priority_keys_kernel<<<div_up(n_vert_h, 256), 256, 0, stream>>>(d_beta_h, d_no_condensation_mask_h,
                                                                         d_row_splits_h, num_rows, n_vert_h,
-                                                                        b.beta_keys, b.event_keys);
+                                                                        d_n_vert_h, b.beta_keys, b.event_keys);
         HGC_LAUNCH_CHECK();
         // stable sort by priority, then stable sort by event: per event, priority order
-        if (int rc = sort_pairs(b.beta_keys, nullptr, b.k1, b.v1, b.tk, b.tv, b.hist, n_vert_h, 32, stream)) return rc;
-        gather_int_kernel<<<div_up(n_vert_h, 256), 256, 0, stream>>>(b.event_keys, b.v1, b.k1, n_vert_h);
+        if (int rc = sort_pairs(b.beta_keys, nullptr, b.k1, b.v1, b.tk, b.tv, b.hist, n_vert_h, 32, stream, d_n_vert_h)) return rc;
+        gather_int_kernel<<<div_up(n_vert_h, 256), 256, 0, stream>>>(b.event_keys, b.v1, b.k1, n_vert_h, d_n_vert_h);
         HGC_LAUNCH_CHECK();
-        if (int rc = sort_pairs(b.k1, b.v1, b.k2, b.v2, b.tk, b.tv, b.hist, n_vert_h, bits_for(num_rows), stream)) return rc;
+        if (int rc = sort_pairs(b.k1, b.v1, b.k2, b.v2, b.tk, b.tv, b.hist, n_vert_h, bits_for(num_rows), stream, d_n_vert_h)) return rc;
 #define HGC_CLAIM(NR)                                                                                       \
     claim_kernel<NR><<<num_rows * kClusterBlocks, kClaimThreads, 0, stream>>>(                                \
             dimensions, d_ccoords_h, d_dist_h, d_no_condensation_mask_h, d_original_indices_h, d_row_splits_h, \
@@ -544,4 +550,26 @@ extern "C" int hgc_binned_assign_to_condensates(
         HGC_LAUNCH_CHECK();
     }
     return HGC_OK;
+}
+}  // namespace hgc
+
+extern "C" int hgc_binned_assign_to_condensates(
+        int dimensions, int dimensions_binning,
+        const float *d_ccoords_h, const float *d_dist_h, const float *d_beta_h,
+        const int *d_no_condensation_mask_h,
+        int *d_high_assigned_status_h,
+        const int *d_original_indices_h, const int *d_row_splits_h,
+        const float *d_ccoords, const float *d_dist, const int *d_no_condensation_mask,
+        const int *d_indices_to_filtered,
+        int *d_assignment, int *d_association, int *d_n_condensates, int *d_alpha_indices,
+        const int *d_bin_splits, const int *d_n_bins, const float *d_bin_widths,
+        const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, int assign_by_max_beta,
+        void *workspace, size_t workspace_bytes, hgc_stream_t stream)
+{
+    return hgc::assign_to_condensates(
+            dimensions, dimensions_binning, d_ccoords_h, d_dist_h, d_beta_h, d_no_condensation_mask_h,
+            d_high_assigned_status_h, d_original_indices_h, d_row_splits_h, d_ccoords, d_dist,
+            d_no_condensation_mask, d_indices_to_filtered, d_assignment, d_association, d_n_condensates,
+            d_alpha_indices, d_bin_splits, d_n_bins, d_bin_widths, d_row_splits, num_rows, n_vert, n_vert_h,
+            nullptr, assign_by_max_beta, workspace, workspace_bytes, stream);
 }

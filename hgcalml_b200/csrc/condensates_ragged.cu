@@ -89,11 +89,12 @@ __global__ void scatter_back_kernel(const int *__restrict__ s_assignment, const 
 // the op lists the condensates first and pads with -1, so entry a of event e moves to
 // n_condensates[e] + (a - row_splits_h[e]).
 __global__ void compact_alpha_kernel(const int *__restrict__ alpha_h, const int *__restrict__ row_splits_h,
-                                     const int *__restrict__ n_condensates, int num_rows, int n_h,
+                                     const int *__restrict__ n_condensates, int num_rows, int n_h_max,
+                                     const int *__restrict__ n_h_dev,
                                      int *__restrict__ alpha_out, unsigned char *__restrict__ is_cond)
 {
     const int a = blockIdx.x * blockDim.x + threadIdx.x;
-    if (a >= n_h) return;
+    if (a >= min(n_h_max, *n_h_dev)) return;
     const int id = alpha_h[a];
     if (id < 0) return;
     int lo = 1, hi = num_rows + 1;  // event = number of row_splits_h[1..num_rows] that are <= a
@@ -191,6 +192,19 @@ struct SizerW {
 }  // namespace
 }  // namespace hgc
 
+namespace hgc {
+int assign_to_condensates(
+        int dimensions, int dimensions_binning,
+        const float *d_ccoords_h, const float *d_dist_h, const float *d_beta_h,
+        const int *d_no_condensation_mask_h, int *d_high_assigned_status_h,
+        const int *d_original_indices_h, const int *d_row_splits_h,
+        const float *d_ccoords, const float *d_dist, const int *d_no_condensation_mask,
+        const int *d_indices_to_filtered,
+        int *d_assignment, int *d_association, int *d_n_condensates, int *d_alpha_indices,
+        const int *d_bin_splits, const int *d_n_bins, const float *d_bin_widths,
+        const int *d_row_splits, int num_rows, int n_vert, int n_vert_h, const int *d_n_vert_h,
+        int assign_by_max_beta, void *workspace, size_t workspace_bytes, hgc_stream_t stream);
+}
 using namespace hgc;
 
 extern "C" size_t hgc_build_and_assign_condensates_workspace_bytes(int n_vert, int dimensions, int n_rs,
@@ -260,15 +274,12 @@ extern "C" int hgc_build_and_assign_condensates(
                                                                           d_row_splits, n_rs, n_vert,
                                                                           b.row_splits_h, b.total);
     HGC_LAUNCH_CHECK();
-    int n_h = 0;
-    HGC_CUDA_TRY(cudaMemcpyAsync(&n_h, b.total, sizeof(int), cudaMemcpyDeviceToHost, stream));
-    HGC_CUDA_TRY(cudaStreamSynchronize(stream));
-    if (n_h < 0 || n_h > n_vert) return HGC_ERR_INVALID_ARGUMENT;
-
-    if (int rc = hgc_binned_assign_to_condensates(
+    // The number of high-beta hits stays on the device: the op is launched for up to n_vert of them
+    // and reads the count itself, so nothing waits for the host here.
+    if (int rc = assign_to_condensates(
                 dimensions, p.cb, b.h_ccoords, b.h_dist, b.h_betas, b.h_mask, b.status_h, b.h_orig, b.row_splits_h,
                 b.s_ccoords, b.s_dist, b.s_mask, b.itf, b.s_assignment, b.s_asso, d_n_condensates, b.alpha_h,
-                nullptr, b.grid->n_bins, &b.grid->bin_width, d_row_splits, num_rows, n_vert, n_h,
+                nullptr, b.grid->n_bins, &b.grid->bin_width, d_row_splits, num_rows, n_vert, n_vert, b.total,
                 assign_by_max_beta, b.op_ws, b.op_ws_bytes, stream_))
         return rc;
 
@@ -277,11 +288,9 @@ extern "C" int hgc_build_and_assign_condensates(
     HGC_LAUNCH_CHECK();
     fill_minus_one_kernel<<<blocks, 256, 0, stream>>>(d_alpha_idx, n_vert);
     HGC_LAUNCH_CHECK();
-    if (n_h > 0) {
-        compact_alpha_kernel<<<div_up(n_h, 256), 256, 0, stream>>>(b.alpha_h, b.row_splits_h, d_n_condensates,
-                                                                   num_rows, n_h, d_alpha_idx, d_is_cond);
-        HGC_LAUNCH_CHECK();
-    }
+    compact_alpha_kernel<<<blocks, 256, 0, stream>>>(b.alpha_h, b.row_splits_h, d_n_condensates, num_rows, n_vert,
+                                                     b.total, d_alpha_idx, d_is_cond);
+    HGC_LAUNCH_CHECK();
     if (h_n_alpha) {
         HGC_CUDA_TRY(cudaMemcpyAsync(h_n_alpha, d_n_condensates + num_rows, sizeof(int), cudaMemcpyDeviceToHost, stream));
         HGC_CUDA_TRY(cudaStreamSynchronize(stream));

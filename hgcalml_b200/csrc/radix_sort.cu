@@ -26,9 +26,11 @@ constexpr int kDigits = 256;
 __device__ __forceinline__ int digit_of(int key, int shift) { return (key >> shift) & (kDigits - 1); }
 
 __global__ void __launch_bounds__(kSortThreads)
-digit_count_kernel(const int *__restrict__ keys, int n, int shift, int *__restrict__ block_hist,
-                   int n_blocks)
+digit_count_kernel(const int *__restrict__ keys, int n_max, const int *__restrict__ n_dev, int shift,
+                   int *__restrict__ block_hist, int n_blocks)
 {
+    // the number of items may sit in device memory (then n_max only sized the grid and the tables)
+    const int n = n_dev ? min(n_max, *n_dev) : n_max;
     __shared__ int counts[kSortWarps][kDigits];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int d = threadIdx.x; d < kSortWarps * kDigits; d += kSortThreads) (&counts[0][0])[d] = 0;
@@ -141,9 +143,10 @@ __global__ void add_tile_offsets_kernel(int *__restrict__ data, int len, const i
 
 __global__ void __launch_bounds__(kSortThreads)
 digit_scatter_kernel(const int *__restrict__ keys_in, const int *__restrict__ vals_in,
-                     int *__restrict__ keys_out, int *__restrict__ vals_out, int n, int shift,
-                     const int *__restrict__ block_offsets, int n_blocks)
+                     int *__restrict__ keys_out, int *__restrict__ vals_out, int n_max,
+                     const int *__restrict__ n_dev, int shift, const int *__restrict__ block_offsets, int n_blocks)
 {
+    const int n = n_dev ? min(n_max, *n_dev) : n_max;
     __shared__ int counts[kSortWarps][kDigits];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int d = threadIdx.x; d < kSortWarps * kDigits; d += kSortThreads) (&counts[0][0])[d] = 0;
@@ -247,7 +250,7 @@ int exclusive_scan_ints(int *data, int len, int *tile_sums, cudaStream_t stream)
 
 int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_out,
                int *keys_tmp, int *vals_tmp, int *block_hist, int n, int key_bits,
-               cudaStream_t stream)
+               cudaStream_t stream, const int *n_dev)
 {
     if (n <= 0) return HGC_OK;
     const int passes = key_bits <= 0 ? 1 : (key_bits + 7) / 8;
@@ -260,11 +263,11 @@ int sort_pairs(const int *keys_in, const int *vals_in, int *keys_out, int *vals_
     const int *src_v = vals_in;
     for (int p = 0; p < passes; p++) {
         const int shift = 8 * p;
-        digit_count_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, n, shift, block_hist, n_blocks);
+        digit_count_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, n, n_dev, shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();
         const int table = kDigits * n_blocks;
         if (int rc = exclusive_scan_ints(block_hist, table, block_hist + table, stream)) return rc;
-        digit_scatter_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, src_v, kbuf[dst], vbuf[dst], n,
+        digit_scatter_kernel<<<n_blocks, kSortThreads, 0, stream>>>(src_k, src_v, kbuf[dst], vbuf[dst], n, n_dev,
                                                                     shift, block_hist, n_blocks);
         HGC_LAUNCH_CHECK();
         src_k = kbuf[dst];

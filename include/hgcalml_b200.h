@@ -12,7 +12,7 @@
  *    caller passes it.  The device that owns `stream` and the d_ pointers must be the calling
  *    thread's current device (cudaSetDevice) when an entry is called.  The entries that wait
  *    for their own stream say so: hgc_workspace_status, hgc_binned_select_knn_static_status and
- *    hgc_build_and_assign_condensates.
+ *    hgc_build_and_assign_condensates when it is asked for the condensate count on the host.
  *  - Return value: HGC_OK or a negative HGC_ERR_* code.  Nothing throws, nothing prints.
  *    Problems that only the device can see (an index outside its table, a bin outside the
  *    grid, an iteration cap reached) set a status word in the workspace, which
@@ -261,8 +261,9 @@ int hgc_binned_assign_to_condensates(
  *          d_n_condensates [n_rs] cumulative count
  *   h_n_alpha (host, may be NULL): receives the number of condensates; the call then returns after
  *          the stream has finished.
- * The number of high-beta hits sizes the op's filtered inputs and is read back once in the middle
- * of the call (one stream synchronisation; the reference's boolean masks do the same). */
+ * The number of high-beta hits never leaves the device (the op's kernels and sorts are launched for
+ * up to n_vert of them and read the count themselves), so with h_n_alpha == NULL the call is a plain
+ * enqueue like every other entry. */
 size_t hgc_build_and_assign_condensates_workspace_bytes(int n_vert, int dimensions, int n_rs, int nbin_dims);
 int hgc_build_and_assign_condensates(
         const float *d_ccoords, const float *d_betas, const float *d_dist, const int *d_no_condensation_mask,
