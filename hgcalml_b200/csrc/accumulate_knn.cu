@@ -363,7 +363,7 @@ int accumulate_dispatch(bool exp_w, const float *w, const float *feat, const int
     const int F4 = F / 4;
 #define HGC_VEC(L, V, C, T, M) return launch_vec<L, V, C, T, M>(exp_w, with_arg, w, feat, idxs, out, out_arg, n_vert, K, ldk, F4, n_out, mm, order, scale, sub_self, stream)
     // lanes per hit x float4 per lane, rows in flight, block size, blocks per SM
-    if (F4 <= 4) HGC_VEC(4, 1, 4, 256, 4);
+    if (F4 <= 4) HGC_VEC(4, 1, 4, 1024, 1);  // measured at F = 16: 2.55 ms against 3.12 ms with 4 blocks of 256 (6.4 M hits)
     if (F4 <= 8) HGC_VEC(8, 1, 4, 256, 4);
     // F = 64: one block of 768 threads per SM works on 96 consecutive hits at a time (measured best on the
     // 64-event batch: the rows those hits share are found in L1)
